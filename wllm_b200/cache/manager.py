@@ -19,6 +19,8 @@ Reference for the bookkeeping this replaces: src/wllm/engine/kv_cache.py:63-303
 (one table per sequence shared by all layers, reserve/advance, free_sequence).
 Pool layout on the device, per group:
     [layer_in_group][k|v][page][kv_head][slot_in_page][head_dim]
+A group whose value heads have a size of their own (`v_head_dim`) holds two pools of that layout
+without the k|v axis, one for keys and one for values.
 """
 from __future__ import annotations
 
@@ -36,6 +38,7 @@ class CacheGroupSpec:
     kv_heads: int
     head_dim: int
     window: int | None = None   # None: every key is kept; n: a token reads the n latest keys (itself included)
+    v_head_dim: int | None = None   # size of a value head when it differs from head_dim
 
 
 @dataclass(frozen=True)
@@ -64,31 +67,39 @@ class CacheGroup:
         self.spec = spec
         self.pool = PagePool(num_pages)
         self.page_size = page_size
-        self.pages = None
+        self.pages = None               # keys and values of one size: one pool with a k|v axis
+        self.key_pages = self.value_pages = None      # value heads of their own size: two pools
         self.poison = poison
+        self.v_head_dim = spec.v_head_dim or spec.head_dim
+        self._item = torch.empty((), dtype=dtype).element_size() if dtype is not None else 4
         if device is not None:
-            shape = (spec.layers, 2, num_pages, spec.kv_heads, page_size, spec.head_dim)
-            self.pages = torch.full(shape, float("nan"), dtype=dtype, device=device) if poison else \
-                torch.zeros(shape, dtype=dtype, device=device)
+            def pool(*shape):
+                return torch.full(shape, float("nan"), dtype=dtype, device=device) if poison else \
+                    torch.zeros(shape, dtype=dtype, device=device)
+            if self.v_head_dim == spec.head_dim:
+                self.pages = pool(spec.layers, 2, num_pages, spec.kv_heads, page_size, spec.head_dim)
+            else:
+                self.key_pages = pool(spec.layers, num_pages, spec.kv_heads, page_size, spec.head_dim)
+                self.value_pages = pool(spec.layers, num_pages, spec.kv_heads, page_size, self.v_head_dim)
 
     def give(self, pages: list) -> None:
         """Pages go back to the pool; with `poison` their contents become NaN first (in stream order, so a step
         still running has read them before)."""
-        if self.poison and self.pages is not None and pages:
-            index = torch.tensor(pages, dtype=torch.long, device=self.pages.device)
-            self.pages.index_fill_(2, index, float("nan"))
+        if self.poison and pages:
+            for pool, axis in ((self.pages, 2), (self.key_pages, 1), (self.value_pages, 1)):
+                if pool is not None:
+                    pool.index_fill_(axis, torch.tensor(pages, dtype=torch.long, device=pool.device), float("nan"))
         for page in pages:
             self.pool.give(page)
 
     def keys(self, layer: int) -> torch.Tensor:
-        return self.pages[layer, 0]
+        return self.pages[layer, 0] if self.pages is not None else self.key_pages[layer]
 
     def values(self, layer: int) -> torch.Tensor:
-        return self.pages[layer, 1]
+        return self.pages[layer, 1] if self.pages is not None else self.value_pages[layer]
 
     def bytes_per_token(self) -> int:
-        item = 4 if self.pages is None else self.pages.element_size()
-        return self.spec.layers * 2 * self.spec.kv_heads * self.spec.head_dim * item
+        return self.spec.layers * self.spec.kv_heads * (self.spec.head_dim + self.v_head_dim) * self._item
 
 
 class StateSlots:

@@ -1,7 +1,8 @@
 """The one registry from an architecture's name to its model.
 
-config.json's `architectures` list is matched against the registered names, first
-match wins, as the reference does (src/wllm/models/registry.py:41-53).  An entry
+config.json's `architectures` list (or its single `architecture` name) is matched
+against the registered names, first match wins, as the reference does
+(src/wllm/models/registry.py:41-53).  An entry
 holds the architecture's configuration class and the function that turns such a
 configuration into a `ModelPlan` (the parts of every layer and the order in which
 layers run); the engine builds the same `ComposedModel` from any plan.
@@ -45,8 +46,18 @@ def resolve_architecture(architectures) -> Architecture:
 def config_from_folder(folder: str):
     """(architecture entry, typed configuration) of a model folder."""
     raw = read_config_json(folder)
-    arch = resolve_architecture(raw.get("architectures") or [])
+    arch = resolve_architecture(named_architectures(raw))
     return arch, arch.config_class.from_dict(raw, where=f"{folder}/config.json")
+
+
+def named_architectures(raw: dict) -> list:
+    """The architecture names of a config.json: the list `architectures`, or the single name `architecture`."""
+    names = raw.get("architectures")
+    if isinstance(names, str):
+        names = [names]
+    if not names and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]
+    return list(names or [])
 
 
 def _load_builtin() -> None:

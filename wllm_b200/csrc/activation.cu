@@ -1,7 +1,7 @@
 // Gated feed-forward activation on a fused [gate | up] row:
 //     out[n, c] = act(gate[n, c]) * up[n, c],   gate = in[n, c], up = in[n, I + c]
 // evaluated in 32-bit and rounded once.  act 0: tanh-approximated GELU
-//     0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)));  act 1: SiLU  x / (1 + exp(-x)).
+//     0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)));  act 1: SiLU  x / (1 + exp(-x));  act 2: ReLU  max(x, 0).
 #include "common.cuh"
 
 __device__ __forceinline__ float act_gelu_tanh(float x) {
@@ -9,6 +9,9 @@ __device__ __forceinline__ float act_gelu_tanh(float x) {
     return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x * x * x)));
 }
 __device__ __forceinline__ float act_silu(float x) { return x / (1.0f + expf(-x)); }
+template <int ACT> __device__ __forceinline__ float act_apply(float x) {
+    return ACT == 0 ? act_gelu_tanh(x) : ACT == 1 ? act_silu(x) : fmaxf(x, 0.f);
+}
 
 template <typename T, int ACT>
 __global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total) {
@@ -16,7 +19,7 @@ __global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, 
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t n = idx / I, c = idx % I;
         const float g = to_f32(in[n * 2 * I + c]), u = to_f32(in[n * 2 * I + I + c]);
-        out[idx] = from_f32<T>((ACT == 0 ? act_gelu_tanh(g) : act_silu(g)) * u);
+        out[idx] = from_f32<T>(act_apply<ACT>(g) * u);
     }
 }
 
@@ -36,8 +39,7 @@ __global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ in, bf16* __res
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
-        o2[i] = __floats2bfloat162_rn((ACT == 0 ? act_gelu_tanh(g.x) : act_silu(g.x)) * u.x,
-                                      (ACT == 0 ? act_gelu_tanh(g.y) : act_silu(g.y)) * u.y);
+        o2[i] = __floats2bfloat162_rn(act_apply<ACT>(g.x) * u.x, act_apply<ACT>(g.y) * u.y);
     }
     *reinterpret_cast<uint4*>(out + (size_t)n * I + c) = ov;
 }
@@ -45,18 +47,19 @@ __global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ in, bf16* __res
 WLLM_API int wllm_gated_act(const void* in, void* out, int dtype, int act, int n, int I, cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (I <= 0) return WLLM_BAD_SIZE;
-    if (act != 0 && act != 1) return WLLM_BAD_SIZE;
+    if (act < 0 || act > 2) return WLLM_BAD_SIZE;
     if (dtype == WLLM_BF16 && I % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         const dim3 grid((I / 8 + 127) / 128, n);
         if (act == 0) return wllm_launch(gated_act_bf16x8_kernel<0>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I);
+        if (act == 2) return wllm_launch(gated_act_bf16x8_kernel<2>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I);
         return wllm_launch(gated_act_bf16x8_kernel<1>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I);
     }
     const size_t total = (size_t)n * I;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
 #define LAUNCH(T, A) wllm_launch(gated_act_kernel<T, A>, blocks, threads, 0, stream, (const T*)in, (T*)out, I, total)
-    if (dtype == WLLM_BF16) return act == 0 ? LAUNCH(bf16, 0) : LAUNCH(bf16, 1);
-    if (dtype == WLLM_F32) return act == 0 ? LAUNCH(float, 0) : LAUNCH(float, 1);
+    if (dtype == WLLM_BF16) return act == 0 ? LAUNCH(bf16, 0) : act == 1 ? LAUNCH(bf16, 1) : LAUNCH(bf16, 2);
+    if (dtype == WLLM_F32) return act == 0 ? LAUNCH(float, 0) : act == 1 ? LAUNCH(float, 1) : LAUNCH(float, 2);
 #undef LAUNCH
     return WLLM_BAD_DTYPE;
 }

@@ -26,6 +26,11 @@
 //            runs its four rows against the tile with the walk's arithmetic.  Portions
 //            of prompts, where neighbouring rows read the same keys.
 //
+// Value heads may have a size of their own (`vd`; the output row of a head has that size), and a head may have a
+// sink: a learned number s_h that joins the softmax's denominator as one more term e^(s_h) with no key and no
+// value, neither scaled nor counted twice.  It enters when a row is finished, after the last chunk was merged:
+//   m' = max(m, s_h);  l' = l e^(m-m') + e^(s_h-m');  out = o e^(m-m') / l'
+//
 // Used for the 32-bit path at every size, and for bfloat16 at the sizes that the
 // tensor-core kernels refuse.
 #include "common.cuh"
@@ -58,7 +63,7 @@ constexpr int CHUNK = 64;
 template <typename T, int NE>
 __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, const T* __restrict__ k_pages,
                                               const T* __restrict__ v_pages, const int* __restrict__ table, int nkv,
-                                              int kvh, int hd, int page_size, int first, int pos, int chunk, float scale,
+                                              int kvh, int hd, int vd, int page_size, int first, int pos, int chunk, float scale,
                                               int lane, float& m, float& l, float (&o)[NE]) {
     m = -INFINITY;
     l = 0.f;
@@ -102,11 +107,11 @@ __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, cons
                 const int j = min(j0 + u, 31);
                 pj[u] = j0 + u < count ? __shfl_sync(0xffffffffu, p, j) : 0.f;
                 const int rj = __shfl_sync(0xffffffffu, row, j);
-                const T* vr = v_pages + (size_t)(rj < 0 || j0 + u >= count ? safe : rj) * hd;
+                const T* vr = v_pages + (size_t)(rj < 0 || j0 + u >= count ? safe : rj) * vd;
 #pragma unroll
                 for (int e = 0; e < NE; ++e) {
                     const int d = e * 32 + lane;
-                    vj[u][e] = d < hd ? to_f32(vr[d]) : 0.f;
+                    vj[u][e] = d < vd ? to_f32(vr[d]) : 0.f;
                 }
             }
 #pragma unroll
@@ -139,6 +144,21 @@ __device__ __forceinline__ void store_row(T* __restrict__ orow, int hd, int lane
         if (d < hd) orow[d] = from_f32<T>(o[e] * inv_l);
     }
 }
+// the same with a sink (null: none) in the denominator
+template <typename T, int NE>
+__device__ __forceinline__ void store_row_sink(T* __restrict__ orow, int vd, int lane, float m, float l, const float (&o)[NE],
+                                               const float* __restrict__ sinks, int head) {
+    if (sinks == nullptr) { store_row<T, NE>(orow, vd, lane, l, o); return; }
+    const float sink = sinks[head];
+    const float m2 = fmaxf(m, sink);
+    const float a = expf(m - m2);
+    const float inv_l = 1.0f / fmaf(l, a, expf(sink - m2));
+#pragma unroll
+    for (int e = 0; e < NE; ++e) {
+        const int d = e * 32 + lane;
+        if (d < vd) orow[d] = from_f32<T>((o[e] * a) * inv_l);
+    }
+}
 
 // SPLIT false: grid (items / WARPS), the warp walks its row's chunks and writes the row.
 // SPLIT true:  grid (items / WARPS, max_chunks), the warp of (item, slot) computes chunk first_chunk + slot of its
@@ -151,7 +171,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
                             const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                             const int* __restrict__ token_req, const int* __restrict__ positions,
                             const int* __restrict__ block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
-                            int page_size, int window, float scale, float* __restrict__ scratch, int max_chunks) {
+                            int page_size, int window, float scale, float* __restrict__ scratch, int max_chunks,
+                            int vd, const float* __restrict__ sinks) {
     extern __shared__ float q_smem[];
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -179,26 +200,27 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     for (int e = 0; e < NE; ++e) o[e] = 0.f;
     for (int chunk = c0; chunk <= c1; ++chunk) {
         float mc, lc, oc[NE];
-        chunk_partial<T, NE>(qs, k_pages, v_pages, table, nkv, kvh, hd, page_size, first, pos, chunk, scale, lane, mc, lc, oc);
+        chunk_partial<T, NE>(qs, k_pages, v_pages, table, nkv, kvh, hd, vd, page_size, first, pos, chunk, scale, lane, mc, lc, oc);
         merge_chunk<NE>(m, l, o, mc, lc, oc);
     }
     if (SPLIT) {
-        float* dst = scratch + ((size_t)item * max_chunks + blockIdx.y) * (hd + 2);
+        float* dst = scratch + ((size_t)item * max_chunks + blockIdx.y) * (vd + 2);
         if (lane == 0) { dst[0] = m; dst[1] = l; }
 #pragma unroll
         for (int e = 0; e < NE; ++e) {
             const int d = e * 32 + lane;
-            if (d < hd) dst[2 + d] = o[e];
+            if (d < vd) dst[2 + d] = o[e];
         }
     } else {
-        store_row<T, NE>(out + (size_t)token * out_stride + (size_t)head * hd, hd, lane, l, o);
+        store_row_sink<T, NE>(out + (size_t)token * out_stride + (size_t)head * vd, vd, lane, m, l, o, sinks, head);
     }
 }
 
 template <typename T, int NE>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_simt_merge_kernel(T* __restrict__ out, int out_stride, const int* __restrict__ positions, int n_tokens,
-                                  int nq, int hd, int window, const float* __restrict__ scratch, int max_chunks) {
+                                  int nq, int hd, int window, const float* __restrict__ scratch, int max_chunks,
+                                  const float* __restrict__ sinks) {
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * WARPS + warp;
@@ -231,14 +253,14 @@ paged_attention_simt_merge_kernel(T* __restrict__ out, int out_stride, const int
         for (int u = 0; u < AHEAD; ++u)
             if (s0 + u < slots) merge_chunk<NE>(m, l, o, mc[u], lc[u], oc[u]);
     }
-    store_row<T, NE>(out + (size_t)token * out_stride + (size_t)head * hd, hd, lane, l, o);
+    store_row_sink<T, NE>(out + (size_t)token * out_stride + (size_t)head * hd, hd, lane, m, l, o, sinks, head);
 }
 
 template <typename T>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                   const int* token_req, const int* positions, const int* block_table, int max_pages, int n_tokens,
                   int nq, int nkv, int hd, int page_size, int window, float scale, float* scratch, int max_chunks,
-                  cudaStream_t stream) {
+                  int vd, const float* sinks, cudaStream_t stream) {
     const int blocks = (n_tokens * nq + WARPS - 1) / WARPS;
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
     const bool split = scratch != nullptr && max_chunks > 1;
@@ -246,17 +268,17 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
         if (!split) \
             return wllm_launch(paged_attention_simt_kernel<T, NE, false>, blocks, WARPS * 32, smem, stream, \
                 (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, positions, \
-                block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks); \
+                block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks); \
         const int st = wllm_launch(paged_attention_simt_kernel<T, NE, true>, dim3(blocks, max_chunks), WARPS * 32, smem, \
                 stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, \
-                positions, block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks); \
+                positions, block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks); \
         if (st != WLLM_OK) return st; \
         return wllm_launch(paged_attention_simt_merge_kernel<T, NE>, blocks, WARPS * 32, 0, stream, (T*)out, out_stride, \
-                positions, n_tokens, nq, hd, window, (const float*)scratch, max_chunks); \
+                positions, n_tokens, nq, vd, window, (const float*)scratch, max_chunks, sinks); \
     } while (0)
-    if (hd <= 64) GO(2);
-    if (hd <= 128) GO(4);
-    if (hd <= 256) GO(8);
+    if (vd <= 64) GO(2);
+    if (vd <= 128) GO(4);
+    if (vd <= 256) GO(8);
     GO(16);
 #undef GO
 }
@@ -264,25 +286,38 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
 // scratch (may be null) and max_chunks: with scratch of n_tokens * nq * max_chunks * (hd + 2) floats and
 // max_chunks > 1 the split kernels run; max_chunks must be at least the number of chunks of 64 keys that any
 // row of the step touches, or the results, still right, are no longer bit-equal to the walk's.
-WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                       const void* v_pages, int dtype, const int* token_req, const int* positions,
-                                       const int* block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
-                                       int page_size, int window, float scale, float* scratch, int max_chunks,
-                                       cudaStream_t stream) {
+// vd: size of a value head (and of a head's output row); sinks: one 32-bit number per query head, or null.
+WLLM_API int wllm_paged_attention_simt_general(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                               const void* v_pages, int dtype, const int* token_req, const int* positions,
+                                               const int* block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
+                                               int page_size, int window, float scale, float* scratch, int max_chunks,
+                                               int vd, const float* sinks, cudaStream_t stream) {
     if (n_tokens <= 0) return WLLM_OK;
-    // rows are read with 16-byte loads: head sizes come in steps of 16 up to 512
-    if (hd <= 0 || hd > 512 || hd % 16 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_pages <= 0)
+    // key rows are read with 16-byte loads: head sizes come in steps of 8 up to 512
+    if (hd <= 0 || hd > 512 || hd % 8 != 0 || vd <= 0 || vd > 512 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 ||
+        max_pages <= 0)
         return WLLM_BAD_SIZE;
     if (scratch != nullptr && (max_chunks < 1 || max_chunks > 65535)) return WLLM_BAD_SIZE;
     if (dtype == WLLM_BF16) {
         if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
         return launch<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
-                            n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, stream);
+                            n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, stream);
     }
     if (dtype == WLLM_F32)
         return launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
-                             n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, stream);
+                             n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, stream);
     return WLLM_BAD_DTYPE;
+}
+
+WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                       const void* v_pages, int dtype, const int* token_req, const int* positions,
+                                       const int* block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
+                                       int page_size, int window, float scale, float* scratch, int max_chunks,
+                                       cudaStream_t stream) {
+    if (hd % 16 != 0) return WLLM_BAD_SIZE;
+    return wllm_paged_attention_simt_general(q, q_stride, out, out_stride, k_pages, v_pages, dtype, token_req, positions,
+                                             block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch,
+                                             max_chunks, hd, nullptr, stream);
 }
 
 // --------------------------------------------------------------------------------------
@@ -302,7 +337,8 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
                                   const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                   const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
                                   const int* __restrict__ req_ctx_len, const int* __restrict__ block_table, int max_pages,
-                                  int nq, int nkv, int hd, int page_size, int window, float scale) {
+                                  int nq, int nkv, int hd, int page_size, int window, float scale, int vd,
+                                  const float* __restrict__ sinks) {
     constexpr int VN = Vec<T>::N;                  // elements of a 16-byte piece
     extern __shared__ __align__(16) unsigned char tl_smem[];
     pdl_begin();
@@ -315,7 +351,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
     const int kld = hd + VN;                       // a key's row in shared memory: the head and one piece of padding (banks)
     float* qs = reinterpret_cast<float*>(tl_smem);                          // [32 rows][hd] float
     T* ks = reinterpret_cast<T*>(qs + TL_ROWS * hd);                        // [2][32 keys][kld]
-    T* vs = ks + 2 * 32 * kld;                                              // [2][32 keys][hd]
+    T* vs = ks + 2 * 32 * kld;                                              // [2][32 keys][vd]
     const int* table = block_table + (size_t)r * max_pages;
 
     // this warp's rows: position, first key, where they are stored
@@ -337,14 +373,14 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
     const int t_lo = key_lo >> 5, t_hi = (key_hi + 31) >> 5;
 
     auto load_tile = [&](int t, int stage) {
-        const int pieces = hd / VN;                // 16-byte pieces of a key's row
+        const int kp = hd / VN, pieces = kp + vd / VN;      // 16-byte pieces of a key's row and of its value's
         for (int c = threadIdx.x; c < 32 * pieces; c += blockDim.x) {
             const int kl = c / pieces, piece = c % pieces, key = t * 32 + kl;
             const bool valid = key >= key_lo && key < key_hi;           // others are zero: their weight is zero, their values must be numbers
             size_t row = 0;
             if (valid) row = ((size_t)table[key / page_size] * nkv + g) * page_size + key % page_size;
-            cp_async_16(ks + ((size_t)stage * 32 + kl) * kld + piece * VN, k_pages + row * hd + piece * VN, valid);
-            cp_async_16(vs + ((size_t)stage * 32 + kl) * hd + piece * VN, v_pages + row * hd + piece * VN, valid);
+            if (piece < kp) cp_async_16(ks + ((size_t)stage * 32 + kl) * kld + piece * VN, k_pages + row * hd + piece * VN, valid);
+            else cp_async_16(vs + ((size_t)stage * 32 + kl) * vd + (piece - kp) * VN, v_pages + row * vd + (piece - kp) * VN, valid);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -365,7 +401,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();                          // tile t is here for everyone (and the queries, the first time)
         const T* kt = ks + (size_t)stage * 32 * kld;
-        const T* vt = vs + (size_t)stage * 32 * hd;
+        const T* vt = vs + (size_t)stage * 32 * vd;
         const int tile = t * 32, key = tile + lane;
         // a row takes part in the tiles from its first key's to its own position's, as in the walk
         bool act[TL_RPW], any = false;
@@ -422,7 +458,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
 #pragma unroll
                 for (int e = 0; e < NE; ++e) {
                     const int d = e * 32 + lane;
-                    v[e] = d < hd ? to_f32(vt[(size_t)j * hd + d]) : 0.f;
+                    v[e] = d < vd ? to_f32(vt[(size_t)j * vd + d]) : 0.f;
                 }
 #pragma unroll
                 for (int i = 0; i < TL_RPW; ++i) {
@@ -449,7 +485,8 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
     for (int i = 0; i < TL_RPW; ++i) {
         const int m = m0 + warp * TL_RPW + i;
         if (m < rows)
-            store_row<T, NE>(out + (size_t)(q_start + m / rep) * out_stride + (size_t)(g * rep + m % rep) * hd, hd, lane, l_t[i], o_t[i]);
+            store_row_sink<T, NE>(out + (size_t)(q_start + m / rep) * out_stride + (size_t)(g * rep + m % rep) * vd, vd, lane,
+                                  m_t[i], l_t[i], o_t[i], sinks, g * rep + m % rep);
     }
 }
 
@@ -457,10 +494,10 @@ template <typename T>
 static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                         const int* req_q_start, const int* req_q_len, const int* req_ctx_len, const int* block_table,
                         int max_pages, int requests, int max_q_len, int nq, int nkv, int hd, int page_size, int window,
-                        float scale, cudaStream_t stream) {
+                        float scale, int vd, const float* sinks, cudaStream_t stream) {
     const int rep = nq / nkv;
     const dim3 grid((max_q_len * rep + TL_ROWS - 1) / TL_ROWS, nkv, requests);
-    const size_t smem = (size_t)TL_ROWS * hd * sizeof(float) + 2 * 32 * ((size_t)(hd + Vec<T>::N) + hd) * sizeof(T);
+    const size_t smem = (size_t)TL_ROWS * hd * sizeof(float) + 2 * 32 * ((size_t)(hd + Vec<T>::N) + vd) * sizeof(T);
 #define GO(NE) do { \
         static bool raised = false; \
         if (!raised) { \
@@ -471,33 +508,46 @@ static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, 
         } \
         return wllm_launch(paged_attention_simt_tiled_kernel<T, NE>, grid, TL_WARPS * 32, smem, stream, (const T*)q, q_stride, \
                            (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, req_q_start, req_q_len, req_ctx_len, \
-                           block_table, max_pages, nq, nkv, hd, page_size, window, scale); \
+                           block_table, max_pages, nq, nkv, hd, page_size, window, scale, vd, sinks); \
     } while (0)
     const int smem_max = TL_ROWS * 256 * (int)sizeof(float) + 2 * 32 * ((256 + Vec<T>::N) + 256) * (int)sizeof(T);
-    if (hd <= 64) GO(2);
-    if (hd <= 128) GO(4);
+    if (vd <= 64) GO(2);
+    if (vd <= 128) GO(4);
     GO(8);
 #undef GO
 }
 
 // The tiled kernel for the requests of a step (all of them: a request with one token is a tile with few rows).
 // Head sizes up to 256; the result is the walk's bit for bit.
-WLLM_API int wllm_paged_attention_simt_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                             const void* v_pages, int dtype, const int* req_q_start, const int* req_q_len,
-                                             const int* req_ctx_len, const int* block_table, int max_pages, int requests,
-                                             int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
-                                             cudaStream_t stream) {
+WLLM_API int wllm_paged_attention_simt_tiled_general(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                                     const void* v_pages, int dtype, const int* req_q_start, const int* req_q_len,
+                                                     const int* req_ctx_len, const int* block_table, int max_pages, int requests,
+                                                     int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
+                                                     int vd, const float* sinks, cudaStream_t stream) {
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
-    if (hd <= 0 || hd > 256 || hd % 16 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_pages <= 0 ||
+    if (hd <= 0 || hd > 256 || hd % 8 != 0 || vd <= 0 || vd > 256 || vd % 8 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_pages <= 0 ||
         nkv > 65535 || requests > 65535)
         return WLLM_BAD_SIZE;
     if (dtype == WLLM_BF16) {
         if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
         return launch_tiled<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
-                                  block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, stream);
+                                  block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, vd, sinks,
+                                  stream);
     }
     if (dtype == WLLM_F32)
         return launch_tiled<float>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
-                                   block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, stream);
+                                   block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, vd, sinks,
+                                   stream);
     return WLLM_BAD_DTYPE;
+}
+
+WLLM_API int wllm_paged_attention_simt_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                             const void* v_pages, int dtype, const int* req_q_start, const int* req_q_len,
+                                             const int* req_ctx_len, const int* block_table, int max_pages, int requests,
+                                             int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
+                                             cudaStream_t stream) {
+    if (hd % 16 != 0) return WLLM_BAD_SIZE;
+    return wllm_paged_attention_simt_tiled_general(q, q_stride, out, out_stride, k_pages, v_pages, dtype, req_q_start, req_q_len,
+                                                   req_ctx_len, block_table, max_pages, requests, max_q_len, nq, nkv, hd,
+                                                   page_size, window, scale, hd, nullptr, stream);
 }

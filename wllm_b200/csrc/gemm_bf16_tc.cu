@@ -41,7 +41,7 @@ template <int AROWS> struct Ring {
 };
 constexpr int NUM_THREADS = 192;
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3, EPI_GATED_RELU = 4 };
 // With k_splits > 1 (32-bit output only) the K range is cut into k_splits parts of whole 64-column
 // blocks; part s of a tile is a work item of its own and writes its partial sum to slab s of C
 // ([k_splits][M][ldc]).  Whoever reads C adds the slabs in order (the norm and rotary kernels do), so the
@@ -67,7 +67,7 @@ __device__ __forceinline__ float epi_silu(float x) { return __fdividef(x, 1.0f +
 template <int EPI, int W>
 __device__ __forceinline__ void drain_chunk(void* __restrict__ c, int ldc, int M, int n_cols, int split, int row, int col,
                                             uint32_t t_chunk, uint32_t up_col) {
-    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
+    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU || EPI == EPI_GATED_RELU;
     uint32_t v[W];
     float f[W];
     tc_ld<W>(t_chunk, v);
@@ -78,7 +78,7 @@ __device__ __forceinline__ void drain_chunk(void* __restrict__ c, int ldc, int M
 #pragma unroll
         for (int i = 0; i < W; ++i) {
             const float g = __uint_as_float(v[i]);
-            f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : epi_silu(g)) * __uint_as_float(u[i]);
+            f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : EPI == EPI_GATED_SILU ? epi_silu(g) : fmaxf(g, 0.f)) * __uint_as_float(u[i]);
         }
     } else {
         tc_wait_ld();
@@ -144,7 +144,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
+    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU || EPI == EPI_GATED_RELU;
     const int n_cols = GATED ? N / 2 : N;                       // columns of the output
     const int tile_n = GATED ? half_rows : 2 * half_rows;       // output columns per tile
     const int UP_COL = half_rows;                               // accumulator column where the second half begins
@@ -326,7 +326,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
+    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU || EPI == EPI_GATED_RELU;
     const int n_cols = GATED ? N / 2 : N;
     const int tile_n = GATED ? half_rows : 2 * half_rows;
     const int UP_COL = half_rows;
@@ -583,7 +583,7 @@ static int launch_pair_as(const CUtensorMap& ma, const CUtensorMap& mw, void* c,
 template <int EPI>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
                        int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream) {
-    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
+    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU || EPI == EPI_GATED_RELU;
     if constexpr (!GATED) {
         if (half_rows > 128)
             return launch_pair_as<EPI, true>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, pairs, stream);
@@ -620,7 +620,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc
 }
 
 // C = A W^T.  epilogue 0: bf16 C [M, N]; 1: fp32 C [M, N]; 2 / 3: W = [gate; up] ([N, K], N even), bf16 C [M, N/2]
-// = gelu_tanh(gate) * up / silu(gate) * up.  `status` is a device int that stays 0 unless a role gave up waiting.
+// = gelu_tanh(gate) * up / silu(gate) * up; 4: relu(gate) * up.  `status` is a device int that stays 0 unless a role gave up waiting.
 // k_splits > 1 needs epilogue 1 and a C of k_splits slabs [M, ldc]; every part must hold at least one block of K.
 // half_rows (a multiple of 16 up to 128; 0 = 128) sets the width of a tile: 2 * half_rows output columns, or
 // half_rows columns of the gated output (by 128 rows, or 256 rows on a pair of CTAs).  On pairs without a gate
@@ -635,7 +635,7 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
     }
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K) return WLLM_BAD_SIZE;
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15)) return WLLM_BAD_ALIGN;
-    const bool gated = epilogue == EPI_GATED_GELU || epilogue == EPI_GATED_SILU;
+    const bool gated = epilogue == EPI_GATED_GELU || epilogue == EPI_GATED_SILU || epilogue == EPI_GATED_RELU;
     if (gated && (N % 2 != 0)) return WLLM_BAD_SIZE;
     const bool pair = M > BM && max_ctas >= 2 && pair_enabled();
     if (half_rows == 0) half_rows = 128;
@@ -659,6 +659,7 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
             case EPI_F32: return launch_pair<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, k_splits, half_rows, status, pairs, stream);
             case EPI_GATED_GELU: return launch_pair<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
             case EPI_GATED_SILU: return launch_pair<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
+            case EPI_GATED_RELU: return launch_pair<EPI_GATED_RELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
         }
         return WLLM_BAD_SIZE;
     }
@@ -669,6 +670,7 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
         case EPI_F32: return launch<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, k_splits, half_rows, status, ctas, stream);
         case EPI_GATED_GELU: return launch<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
         case EPI_GATED_SILU: return launch<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
+        case EPI_GATED_RELU: return launch<EPI_GATED_RELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
     }
     return WLLM_BAD_SIZE;
 }

@@ -1,0 +1,265 @@
+// Linear attention with a decayed matrix state per (request, head):
+//
+//     S_t = diag(a_t) S_(t-1) + k_t v_t^T          S: [dim, vdim], 32-bit, one per request and head
+//     o_t = S_t^T q_t
+//
+// a_t is a decay per key channel and token (gated linear attention) or one constant per head (retention).
+// The state lives in the cache manager's state slots and is carried from step to step; a request's tokens of
+// one step are walked in order from the state that the step before left, so a whole prompt, a portion and a
+// single decoded token are one case and give the same bits.
+//
+// Three entry points, all 32-bit inside:
+//   wllm_linattn_prepare    from a fused projection row (q | k | v | ... in one matrix product, possibly still in
+//                           split-K slabs): q and k turned by the rotary angle of the token's position (optional),
+//                           scaled, v copied, and the decay of every key channel worked out from a low-rank map:
+//                               z = W2 (x W1^T) + b,   a = sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau)
+//   wllm_linattn_scan       the recurrence.  Grid (tiles of 32 value columns, heads, requests); a lane owns one
+//                           column of S, a warp a run of at most 16 key channels of it, in registers.  Tokens
+//                           arrive in tiles of 8 through a two-stage cp.async ring; the warps' partial dot products of a
+//                           token meet in shared memory and are added in warp order.
+//   wllm_head_gate_norm     per head: o / sqrt(mean(o^2) + eps) [* w] * silu(g), rounded once to the matrix type
+//                           (the operand of the output projection).
+#include "common.cuh"
+
+__device__ __forceinline__ float la_any(const void* p, int dtype, size_t i) {
+    return dtype == WLLM_BF16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i]) : reinterpret_cast<const float*>(p)[i];
+}
+// element i of a row that may come as `parts` slabs `stride` elements apart, added in slab order
+__device__ __forceinline__ float la_in(const void* p, int dtype, int parts, size_t stride, size_t i) {
+    float v = la_any(p, dtype, i);
+    for (int s = 1; s < parts; ++s) v += la_any(p, dtype, i + (size_t)s * stride);
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// prepare: grid (tokens, heads)
+// ---------------------------------------------------------------------------------------------------
+__global__ void linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_stride, int parts, size_t part_stride,
+                                       int q_off, int k_off, int v_off, int a_off, int H, int D, int V, int rank,
+                                       const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim,
+                                       float q_scale, float k_scale, const void* __restrict__ w2, const void* __restrict__ b2,
+                                       int w_dtype, float inv_tau, float* __restrict__ q, float* __restrict__ k,
+                                       float* __restrict__ v, float* __restrict__ decay) {
+    extern __shared__ float low[];               // the low-rank vector of the token
+    pdl_launch_dependents();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float pos = (float)positions[t];
+    const int half = rot_dim >> 1;
+    pdl_wait();
+    const size_t row = (size_t)t * row_stride;
+    if (a_off >= 0) {
+        for (int r = threadIdx.x; r < rank; r += blockDim.x) low[r] = la_in(fused, in_dtype, parts, part_stride, row + a_off + r);
+        __syncthreads();
+    }
+    for (int which = 0; which < 2; ++which) {
+        const int off = (which ? k_off : q_off) + h * D;
+        float* dst = (which ? k : q) + ((size_t)t * H + h) * D;
+        const float scale = which ? k_scale : q_scale;
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            float sn, cs, y1, y2;
+            sincosf(pos * inv_freq[j], &sn, &cs);
+            rotate_pair(la_in(fused, in_dtype, parts, part_stride, row + off + j),
+                        la_in(fused, in_dtype, parts, part_stride, row + off + j + half), sn, cs, y1, y2);
+            dst[j] = y1 * scale;
+            dst[j + half] = y2 * scale;
+        }
+        for (int c = rot_dim + threadIdx.x; c < D; c += blockDim.x)
+            dst[c] = la_in(fused, in_dtype, parts, part_stride, row + off + c) * scale;
+    }
+    for (int c = threadIdx.x; c < V; c += blockDim.x)
+        v[((size_t)t * H + h) * V + c] = la_in(fused, in_dtype, parts, part_stride, row + v_off + h * V + c);
+    if (a_off >= 0) {
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            const size_t ch = (size_t)h * D + c;
+            float z = la_any(b2, w_dtype, ch);
+            for (int r = 0; r < rank; ++r) z = fmaf(low[r], la_any(w2, w_dtype, ch * rank + r), z);
+            // log(sigmoid(z)) = min(z, 0) - log(1 + e^-|z|), exact at both ends
+            const float log_sig = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+            decay[((size_t)t * H + h) * D + c] = expf(log_sig * inv_tau);
+        }
+    }
+}
+
+WLLM_API int wllm_linattn_prepare(const void* fused, int in_dtype, int row_stride, int parts, long long part_stride, int q_off,
+                                  int k_off, int v_off, int a_off, int n, int H, int D, int V, int rank, const int* positions,
+                                  const float* inv_freq, int rot_dim, float q_scale, float k_scale, const void* w2,
+                                  const void* b2, int w_dtype, float tau, float* q, float* k, float* v, float* decay,
+                                  cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (H <= 0 || H > 65535 || D <= 0 || V <= 0 || parts < 1 || rot_dim < 0 || rot_dim > D || (rot_dim & 1)) return WLLM_BAD_SIZE;
+    if (a_off >= 0 && (rank <= 0 || rank > 8192 || !(tau > 0.f) || !w2 || !b2 || !decay)) return WLLM_BAD_SIZE;
+    if ((in_dtype != WLLM_BF16 && in_dtype != WLLM_F32) || (a_off >= 0 && w_dtype != WLLM_BF16 && w_dtype != WLLM_F32))
+        return WLLM_BAD_DTYPE;
+    const int threads = D >= 128 ? 128 : 64;
+    return wllm_launch(linattn_prepare_kernel, dim3(n, H), threads, a_off >= 0 ? (size_t)rank * sizeof(float) : 0, stream, fused,
+                       in_dtype, row_stride, parts, (size_t)part_stride, q_off, k_off, v_off, a_off, H, D, V, rank, positions,
+                       inv_freq, rot_dim, q_scale, k_scale, w2, b2, w_dtype, a_off >= 0 ? 1.0f / tau : 0.f, q, k, v, decay);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// scan
+// ---------------------------------------------------------------------------------------------------
+constexpr int LA_CPT = 16;       // key channels a thread holds of its column of S
+constexpr int LA_TT = 8;         // tokens of a tile
+constexpr int LA_COLS = 32;      // value columns of a CTA (one a lane)
+
+__device__ __forceinline__ void la_cp4(float* smem_dst, const float* src) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+
+template <bool PER_CHANNEL>
+__global__ void __launch_bounds__(1024)
+linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                    const float* __restrict__ decay, const float* __restrict__ head_decay, float* __restrict__ state,
+                    float* __restrict__ out, const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
+                    const int* __restrict__ req_slot, int H, int D, int V, int cpt) {
+    extern __shared__ float la_smem[];
+    pdl_begin();
+    const int r = blockIdx.z, h = blockIdx.y;
+    const int q_len = req_q_len[r], slot = req_slot[r];
+    if (q_len <= 0 || slot < 0) return;                       // a request that brings no token
+    const int t0 = req_q_start[r];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int j = blockIdx.x * LA_COLS + lane;                // this lane's column of S
+    const bool col = j < V;
+    const int c_lo = warp * cpt, c_hi = min(D, c_lo + cpt);   // this warp's key channels
+    // shared memory: two stages of [q | k | (a) | v] for LA_TT tokens, then two rounds of the warps' partial sums
+    const int per_token = (PER_CHANNEL ? 3 : 2) * D + LA_COLS;
+    float* stage0 = la_smem;
+    float* red = la_smem + 2 * LA_TT * per_token;             // [2][warps][32]
+
+    float S[LA_CPT];
+    float* Sg = state + (((size_t)slot * H + h) * D) * V;
+#pragma unroll
+    for (int i = 0; i < LA_CPT; ++i) S[i] = (col && c_lo + i < c_hi) ? Sg[(size_t)(c_lo + i) * V + j] : 0.f;
+    const float fixed = PER_CHANNEL ? 0.f : head_decay[h];
+
+    auto load_tile = [&](int tile, int stage) {
+        float* dst = stage0 + (size_t)stage * LA_TT * per_token;
+        const int first = t0 + tile * LA_TT, count = min(LA_TT, q_len - tile * LA_TT);
+        for (int idx = threadIdx.x; idx < count * per_token; idx += blockDim.x) {
+            const int tt = idx / per_token, e = idx % per_token;
+            const size_t tok = (size_t)(first + tt);
+            const float* src;
+            if (e < D) src = q + (tok * H + h) * D + e;
+            else if (e < 2 * D) src = k + (tok * H + h) * D + (e - D);
+            else if (PER_CHANNEL && e < 3 * D) src = decay + (tok * H + h) * D + (e - 2 * D);
+            else {
+                const int cc = blockIdx.x * LA_COLS + (e - (PER_CHANNEL ? 3 : 2) * D);
+                src = v + (tok * H + h) * V + min(cc, V - 1);
+            }
+            la_cp4(dst + idx, src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    const int tiles = (q_len + LA_TT - 1) / LA_TT;
+    load_tile(0, 0);
+    int round = 0;
+    for (int tile = 0; tile < tiles; ++tile) {
+        const int stage = tile & 1;
+        if (tile + 1 < tiles) {
+            load_tile(tile + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const float* base = stage0 + (size_t)stage * LA_TT * per_token;
+        const int count = min(LA_TT, q_len - tile * LA_TT);
+        for (int tt = 0; tt < count; ++tt) {
+            const float* qs = base + tt * per_token;
+            const float* ks = qs + D;
+            const float* as = ks + D;
+            const float vj = qs[(PER_CHANNEL ? 3 : 2) * D + lane];
+            float partial = 0.f;
+#pragma unroll
+            for (int i = 0; i < LA_CPT; ++i) {
+                if (c_lo + i < c_hi) {
+                    const float a = PER_CHANNEL ? as[c_lo + i] : fixed;
+                    S[i] = fmaf(a, S[i], ks[c_lo + i] * vj);
+                    partial = fmaf(S[i], qs[c_lo + i], partial);
+                }
+            }
+            red[(round * warps + warp) * 32 + lane] = partial;
+            __syncthreads();
+            if (warp == 0 && col) {
+                float o = red[(round * warps) * 32 + lane];
+                for (int w = 1; w < warps; ++w) o += red[(round * warps + w) * 32 + lane];
+                out[((size_t)(t0 + tile * LA_TT + tt) * H + h) * V + j] = o;
+            }
+            round ^= 1;
+        }
+    }
+    if (col) {
+#pragma unroll
+        for (int i = 0; i < LA_CPT; ++i)
+            if (c_lo + i < c_hi) Sg[(size_t)(c_lo + i) * V + j] = S[i];
+    }
+}
+
+// q, k: [n, H, D]; v, out: [n, H, V]; decay: [n, H, D] per key channel, or null with head_decay [H];
+// state: [slots, H, D, V].  Requests by start, length and state slot; a length of 0 or a slot of -1 is passed by.
+WLLM_API int wllm_linattn_scan(const float* q, const float* k, const float* v, const float* decay, const float* head_decay,
+                               float* state, float* out, const int* req_q_start, const int* req_q_len, const int* req_slot,
+                               int requests, int H, int D, int V, cudaStream_t stream) {
+    if (requests <= 0) return WLLM_OK;
+    if (H <= 0 || H > 65535 || requests > 65535 || D <= 0 || D > 32 * LA_CPT || V <= 0) return WLLM_BAD_SIZE;
+    if (!decay && !head_decay) return WLLM_BAD_SIZE;
+    const int warps = (D + LA_CPT - 1) / LA_CPT;
+    const int cpt = (D + warps - 1) / warps;
+    const dim3 grid((V + LA_COLS - 1) / LA_COLS, H, requests);
+    const size_t smem = ((size_t)2 * LA_TT * ((decay ? 3 : 2) * D + LA_COLS) + 2 * warps * 32) * sizeof(float);
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(linattn_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linattn_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        raised = true;
+    }
+    if (decay)
+        return wllm_launch(linattn_scan_kernel<true>, grid, warps * 32, smem, stream, q, k, v, decay, head_decay, state, out,
+                           req_q_start, req_q_len, req_slot, H, D, V, cpt);
+    return wllm_launch(linattn_scan_kernel<false>, grid, warps * 32, smem, stream, q, k, v, decay, head_decay, state, out,
+                       req_q_start, req_q_len, req_slot, H, D, V, cpt);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// head norm and gate: grid (tokens, heads), one warp
+// ---------------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void head_gate_norm_kernel(const float* __restrict__ o, const void* __restrict__ fused, int in_dtype, int row_stride,
+                                      int parts, size_t part_stride, int g_off, const void* __restrict__ w, int w_dtype,
+                                      float eps, TO* __restrict__ out, int H, int V) {
+    pdl_begin();
+    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+    const float* orow = o + ((size_t)t * H + h) * V;
+    float ss = 0.f;
+    for (int c = lane; c < V; c += 32) ss = fmaf(orow[c], orow[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+    const size_t grow = (size_t)t * row_stride + g_off + (size_t)h * V;
+    for (int c = lane; c < V; c += 32) {
+        const float g = la_in(fused, in_dtype, parts, part_stride, grow + c);
+        float y = orow[c] * inv;
+        if (w) y *= la_any(w, w_dtype, c);
+        out[((size_t)t * H + h) * V + c] = from_f32<TO>(y * (g / (1.0f + expf(-g))));
+    }
+}
+
+// out[n, H*V] = o / sqrt(mean_V(o^2) + eps) * w[V] (w may be null) * silu(g), g = fused[:, g_off + h*V + c]
+WLLM_API int wllm_head_gate_norm(const float* o, const void* fused, int in_dtype, int row_stride, int parts,
+                                 long long part_stride, int g_off, const void* w, int w_dtype, float eps, void* out,
+                                 int out_dtype, int n, int H, int V, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (H <= 0 || H > 65535 || V <= 0 || parts < 1) return WLLM_BAD_SIZE;
+    if ((in_dtype != WLLM_BF16 && in_dtype != WLLM_F32) || (w && w_dtype != WLLM_BF16 && w_dtype != WLLM_F32)) return WLLM_BAD_DTYPE;
+    if (out_dtype == WLLM_BF16)
+        return wllm_launch(head_gate_norm_kernel<bf16>, dim3(n, H), 32, 0, stream, o, fused, in_dtype, row_stride, parts,
+                           (size_t)part_stride, g_off, w, w_dtype, eps, (bf16*)out, H, V);
+    if (out_dtype == WLLM_F32)
+        return wllm_launch(head_gate_norm_kernel<float>, dim3(n, H), 32, 0, stream, o, fused, in_dtype, row_stride, parts,
+                           (size_t)part_stride, g_off, w, w_dtype, eps, (float*)out, H, V);
+    return WLLM_BAD_DTYPE;
+}

@@ -8,6 +8,11 @@
 // the kernel reads row rows[i] and writes row i (the final norm at the places whose
 // logits are wanted) and leaves the residual untouched.  One block per row; the sum
 // of squares is reduced in a fixed order that depends on nothing but the row.
+// With `center` the row's mean is taken off first (a layer norm without a bias):
+//     out[i] = (r - mean(r)) / sqrt(mean((r - mean)^2) + eps) * (offset + w)
+// `wllm_branch_norm` norms a branch output (or two of them) that is not yet part of the residual:
+//     out = factor * (norm(a) * wa  [+ norm(b) * wb]),   32-bit out
+// which is the norm behind a sublayer of a block that norms on both sides, and the mean of two mixers.
 #include "common.cuh"
 
 template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]);
@@ -68,7 +73,7 @@ __device__ __forceinline__ void add_parts(float (&v)[4], const TD* __restrict__ 
 template <typename TD, typename TW, typename TO, int VEC, int VPT>
 __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, int delta_splits,
                                size_t delta_split_stride, const TW* __restrict__ w, float eps, float offset,
-                               TO* __restrict__ out, const int* __restrict__ rows, int H) {
+                               TO* __restrict__ out, const int* __restrict__ rows, int H, int center) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     constexpr bool one_pass = VEC == 4 && VPT > 0;
@@ -91,7 +96,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
     TO* o = out + (size_t)i * H;
     if (one_pass) {
         float v[NV][4];
-        float ss = 0.f;
+        float ss = 0.f, sum = 0.f;
 #pragma unroll
         for (int k = 0; k < NV; ++k) {
             const int c = (threadIdx.x + k * blockDim.x) * 4;
@@ -100,7 +105,16 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
                 load4(r + c, v[k]);
                 if (d) add_parts<TD, 4>(v[k], d + c, delta_splits, delta_split_stride);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) ss += v[k][e] * v[k][e];
+                for (int e = 0; e < 4; ++e) sum += v[k][e];
+            }
+        }
+        const float mean = center ? block_sum(sum, scratch) / (float)H : 0.f;     // (x - 0) is x, bit for bit
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = (threadIdx.x + k * blockDim.x) * 4;
+            if (c < H) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ss += (v[k][e] - mean) * (v[k][e] - mean);
             }
         }
         ss = block_sum(ss, scratch);
@@ -112,11 +126,23 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
                 float y[4];
                 if (write_back) store4(r + c, v[k]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) y[e] = (v[k][e] * inv) * (offset + wv[k][e]);
+                for (int e = 0; e < 4; ++e) y[e] = ((v[k][e] - mean) * inv) * (offset + wv[k][e]);
                 store4(o + c, y);
             }
         }
         return;
+    }
+    float mean = 0.f;
+    if (center) {
+        float sum = 0.f;
+        for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (VEC == 4) load4(r + c, v); else v[0] = r[c];
+            if (d) add_parts<TD, VEC>(v, d + c, delta_splits, delta_split_stride);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) sum += v[k];
+        }
+        mean = block_sum(sum, scratch) / (float)H;
     }
     float ss = 0.f;
     for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
@@ -124,7 +150,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
         if (VEC == 4) load4(r + c, v); else v[0] = r[c];
         if (d) add_parts<TD, VEC>(v, d + c, delta_splits, delta_split_stride);
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) ss += v[k] * v[k];
+        for (int k = 0; k < VEC; ++k) ss += (v[k] - mean) * (v[k] - mean);
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
@@ -138,21 +164,21 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
         }
         float y[4];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) y[k] = (v[k] * inv) * (offset + wv[k]);
+        for (int k = 0; k < VEC; ++k) y[k] = ((v[k] - mean) * inv) * (offset + wv[k]);
         if (VEC == 4) store4(o + c, y); else o[c] = from_f32<TO>(y[0]);
     }
 }
 
 template <typename TD, typename TW>
 static int launch_out(float* resid, const void* delta, int delta_splits, size_t delta_split_stride, const void* w, float eps,
-                      float offset, void* out, int out_dtype, const int* rows, int n, int H, cudaStream_t stream) {
+                      float offset, void* out, int out_dtype, const int* rows, int n, int H, int center, cudaStream_t stream) {
     const bool vec = H % 4 == 0 && ((uintptr_t)resid & 15) == 0 && ((uintptr_t)delta & 15) == 0 &&
                      ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0 && delta_split_stride % 4 == 0;
     const int per = vec ? 4 : 1;
     const int threads = H / per >= 512 ? 512 : (H / per >= 256 ? 256 : 128);   // one vector a thread up to 2048 columns
     const int vpt = !vec ? 0 : (H <= threads * 4 ? 1 : (H <= threads * 8 ? 2 : (H <= threads * 16 ? 4 : 0)));
 #define GO(TO, V, P) wllm_launch(rmsnorm_kernel<TD, TW, TO, V, P>, n, threads, 0, stream, resid, (const TD*)delta, delta_splits, \
-                       delta_split_stride, (const TW*)w, eps, offset, (TO*)out, rows, H)
+                       delta_split_stride, (const TW*)w, eps, offset, (TO*)out, rows, H, center)
 #define PICK(TO) (vpt == 1 ? GO(TO, 4, 1) : vpt == 2 ? GO(TO, 4, 2) : vpt == 4 ? GO(TO, 4, 4) : vec ? GO(TO, 4, 0) : GO(TO, 1, 0))
     if (out_dtype == WLLM_BF16) return PICK(bf16);
     if (out_dtype == WLLM_F32) return PICK(float);
@@ -161,15 +187,85 @@ static int launch_out(float* resid, const void* delta, int delta_splits, size_t 
     return WLLM_BAD_DTYPE;
 }
 
-WLLM_API int wllm_rmsnorm(float* resid, const void* delta, int delta_dtype, int delta_splits, long long delta_split_stride,
-                          const void* w, int w_dtype, float eps, float offset, void* out, int out_dtype, const int* rows,
-                          int n, int H, cudaStream_t stream) {
+// center 0: root-mean-square norm; 1: the mean is taken off first (layer norm without a bias).
+WLLM_API int wllm_norm(float* resid, const void* delta, int delta_dtype, int delta_splits, long long delta_split_stride,
+                       const void* w, int w_dtype, float eps, float offset, int center, void* out, int out_dtype,
+                       const int* rows, int n, int H, cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (H <= 0 || delta_splits < 1 || delta_split_stride < 0) return WLLM_BAD_SIZE;
     const bool dbf = delta_dtype == WLLM_BF16, wbf = w_dtype == WLLM_BF16;
     if ((delta_dtype != WLLM_BF16 && delta_dtype != WLLM_F32) || (w_dtype != WLLM_BF16 && w_dtype != WLLM_F32)) return WLLM_BAD_DTYPE;
-    if (dbf && wbf) return launch_out<bf16, bf16>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, stream);
-    if (dbf && !wbf) return launch_out<bf16, float>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, stream);
-    if (!dbf && wbf) return launch_out<float, bf16>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, stream);
-    return launch_out<float, float>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, stream);
+    center = center ? 1 : 0;
+    if (dbf && wbf) return launch_out<bf16, bf16>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, center, stream);
+    if (dbf && !wbf) return launch_out<bf16, float>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, center, stream);
+    if (!dbf && wbf) return launch_out<float, bf16>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, center, stream);
+    return launch_out<float, float>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, center, stream);
+}
+
+WLLM_API int wllm_rmsnorm(float* resid, const void* delta, int delta_dtype, int delta_splits, long long delta_split_stride,
+                          const void* w, int w_dtype, float eps, float offset, void* out, int out_dtype, const int* rows,
+                          int n, int H, cudaStream_t stream) {
+    return wllm_norm(resid, delta, delta_dtype, delta_splits, delta_split_stride, w, w_dtype, eps, offset, 0, out, out_dtype,
+                     rows, n, H, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The norm of a branch output (or of two, added): one block per row, every pass reads the parts again
+// (they lie in the L2) and adds them in slab order, so that no row length is too long for it.
+// ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float any_at(const void* p, int dtype, size_t i) {
+    return dtype == WLLM_BF16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i]) : reinterpret_cast<const float*>(p)[i];
+}
+__device__ __forceinline__ float parts_at(const void* p, int dtype, int parts, size_t stride, size_t i) {
+    float v = any_at(p, dtype, i);
+    for (int s = 1; s < parts; ++s) v += any_at(p, dtype, i + (size_t)s * stride);
+    return v;
+}
+// (mean, 1 / sqrt(var + eps)) of one row of a branch
+__device__ __forceinline__ void branch_stats(const void* p, int dtype, int parts, size_t stride, size_t row0, int H, int center,
+                                             float eps, float* scratch, float& mean, float& inv) {
+    mean = 0.f;
+    if (center) {
+        float sum = 0.f;
+        for (int c = threadIdx.x; c < H; c += blockDim.x) sum += parts_at(p, dtype, parts, stride, row0 + c);
+        mean = block_sum(sum, scratch) / (float)H;
+    }
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = parts_at(p, dtype, parts, stride, row0 + c) - mean;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    inv = 1.0f / sqrtf(ss / (float)H + eps);
+}
+
+__global__ void branch_norm_kernel(const void* __restrict__ a, int a_dtype, int a_parts, size_t a_stride, const void* __restrict__ wa,
+                                   const void* __restrict__ b, int b_dtype, int b_parts, size_t b_stride, const void* __restrict__ wb,
+                                   int w_dtype, float eps, int center, float factor, float* __restrict__ out, int H) {
+    __shared__ float scratch[32];
+    pdl_begin();
+    const size_t row0 = (size_t)blockIdx.x * H;
+    float mean_a, inv_a, mean_b = 0.f, inv_b = 0.f;
+    branch_stats(a, a_dtype, a_parts, a_stride, row0, H, center, eps, scratch, mean_a, inv_a);
+    if (b) branch_stats(b, b_dtype, b_parts, b_stride, row0, H, center, eps, scratch, mean_b, inv_b);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float y = ((parts_at(a, a_dtype, a_parts, a_stride, row0 + c) - mean_a) * inv_a) * any_at(wa, w_dtype, c);
+        if (b) y += ((parts_at(b, b_dtype, b_parts, b_stride, row0 + c) - mean_b) * inv_b) * any_at(wb, w_dtype, c);
+        out[row0 + c] = y * factor;
+    }
+}
+
+// out[n, H] (32-bit) = factor * (norm(a) * wa + norm(b) * wb); b and wb may be null.  a and b are [n, H] tensors of either
+// element type or `parts` 32-bit slabs `stride` elements apart; the gains share one element type.
+WLLM_API int wllm_branch_norm(const void* a, int a_dtype, int a_parts, long long a_stride, const void* wa,
+                              const void* b, int b_dtype, int b_parts, long long b_stride, const void* wb, int w_dtype,
+                              float eps, int center, float factor, float* out, int n, int H, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (H <= 0 || a_parts < 1 || (b && b_parts < 1)) return WLLM_BAD_SIZE;
+    if ((a_dtype != WLLM_BF16 && a_dtype != WLLM_F32) || (w_dtype != WLLM_BF16 && w_dtype != WLLM_F32) ||
+        (b && b_dtype != WLLM_BF16 && b_dtype != WLLM_F32))
+        return WLLM_BAD_DTYPE;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    return wllm_launch(branch_norm_kernel, n, threads, 0, stream, a, a_dtype, a_parts, (size_t)a_stride, wa, b, b_dtype,
+                       b_parts, (size_t)b_stride, wb, w_dtype, eps, center ? 1 : 0, factor, out, H);
 }

@@ -9,8 +9,11 @@
 // [n, nq * hd].  The input row may come as `in_splits` partial sums (slabs `in_split_stride` elements
 // apart, as the split-K matrix product leaves them), which are added in slab order first.  A token
 // whose slot is negative writes nothing to the cache (a layer that reads another layer's cache).
+// Value heads may have a size of their own (`vd`): the fused row is nq heads of hd, nkv heads of hd, nkv heads
+// of vd.  With `unit_norm` every rotated query and key head is divided by its root mean square,
+// y / sqrt(mean(y^2) + norm_eps), in 32-bit, before it is rounded and stored.
 //
-// Page layout: [page][kv_head][slot_in_page][head_dim]; `slots[n]` is page * page_size + slot_in_page.
+// Page layout: [page][kv_head][slot_in_page][head_dim] (values: [..][vd]); `slots[n]` is page * page_size + slot_in_page.
 #include "common.cuh"
 
 // Two launch shapes.  Fewer than 1,024 tokens (a decode step, a short prompt): grid (token, head), so that the heads of a token run on
@@ -24,7 +27,8 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
                                      TO* __restrict__ q_out, int q_stride, const int* __restrict__ positions,
                                      const int* __restrict__ slots, const float* __restrict__ inv_freq,
                                      TO* __restrict__ k_pages, TO* __restrict__ v_pages, int nq, int nkv, int hd,
-                                     int rot_dim, int page_size, int interleaved) {
+                                     int rot_dim, int page_size, int interleaved, int vd, int unit_norm, float norm_eps) {
+    extern __shared__ float head_buf[];      // unit_norm: [hd] the rotated head, then 32 floats for the reduction
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const int slot = slots ? slots[t] : -1;
@@ -36,15 +40,16 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
     pdl_wait();
     const int h_lo = ALL_HEADS ? 0 : blockIdx.y, h_hi = ALL_HEADS ? nq + 2 * nkv : blockIdx.y + 1;
     for (int h = h_lo; h < h_hi; ++h) {
-        const TI* x = qkv + (size_t)t * row_stride + (size_t)h * hd;
+        const bool value = h >= nq + nkv;
+        const TI* x = qkv + (size_t)t * row_stride + (value ? (size_t)(nq + nkv) * hd + (size_t)(h - nq - nkv) * vd : (size_t)h * hd);
         TO* dst;
         if (h < nq) {
             dst = q_out + (size_t)t * q_stride + (size_t)h * hd;
         } else {
             if (slot < 0) break;
-            const int kvh = h < nq + nkv ? h - nq : h - nq - nkv;
-            TO* pages = h < nq + nkv ? k_pages : v_pages;
-            dst = pages + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * hd;
+            const int kvh = value ? h - nq - nkv : h - nq;
+            TO* pages = value ? v_pages : k_pages;
+            dst = pages + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * (value ? vd : hd);
         }
         auto in = [&](int c) {     // part 0 + part 1 + ... in order; sixteen loads are in flight at a time
             if (in_splits == 1) return to_f32(x[c]);
@@ -59,8 +64,31 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
             }
             return v;
         };
-        if (h >= nq + nkv) {
-            for (int c = threadIdx.x; c < hd; c += blockDim.x) dst[c] = from_f32<TO>(in(c));
+        if (value) {
+            for (int c = threadIdx.x; c < vd; c += blockDim.x) dst[c] = from_f32<TO>(in(c));
+            continue;
+        }
+        if (unit_norm) {         // the same turn, kept in 32-bit until the head's mean square is known
+            float ss = 0.f;
+            for (int j = threadIdx.x; j < half; j += blockDim.x) {
+                float sn = s0, cs = c0;
+                if (j != (int)threadIdx.x) sincosf(pos * inv_freq[j], &sn, &cs);
+                const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+                float y1, y2;
+                rotate_pair(in(ia), in(ib), sn, cs, y1, y2);
+                head_buf[ia] = y1;
+                head_buf[ib] = y2;
+                ss += y1 * y1 + y2 * y2;
+            }
+            for (int c = rot_dim + threadIdx.x; c < hd; c += blockDim.x) {
+                const float y = in(c);
+                head_buf[c] = y;
+                ss += y * y;
+            }
+            ss = block_sum(ss, head_buf + hd);
+            const float inv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
+            for (int c = threadIdx.x; c < hd; c += blockDim.x) dst[c] = from_f32<TO>(head_buf[c] * inv);
+            __syncthreads();     // the buffer is free for the next head
             continue;
         }
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
@@ -136,14 +164,16 @@ __global__ void rope_kv_write_rows_kernel(const bf16* __restrict__ qkv, int row_
     }
 }
 
-WLLM_API int wllm_rope_kv_write(const void* qkv, int in_dtype, int row_stride, int in_splits, long long in_split_stride,
-                                void* q_out, int out_dtype, int q_stride, const int* positions, const int* slots,
-                                const float* inv_freq, void* k_pages, void* v_pages, int n, int nq, int nkv, int hd,
-                                int rot_dim, int page_size, int interleaved, cudaStream_t stream) {
+// vd: size of a value head (hd when they are the same); unit_norm: divide rotated q and k heads by their root mean square.
+WLLM_API int wllm_rope_kv_write_general(const void* qkv, int in_dtype, int row_stride, int in_splits, long long in_split_stride,
+                                        void* q_out, int out_dtype, int q_stride, const int* positions, const int* slots,
+                                        const float* inv_freq, void* k_pages, void* v_pages, int n, int nq, int nkv, int hd,
+                                        int rot_dim, int page_size, int interleaved, int vd, int unit_norm, float norm_eps,
+                                        cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
-    if (hd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv <= 0 || in_splits < 1)
+    if (hd <= 0 || vd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv <= 0 || in_splits < 1)
         return WLLM_BAD_SIZE;
-    if (n >= 256 && !interleaved && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && rot_dim % 16 == 0 &&
+    if (n >= 256 && !interleaved && vd == hd && !unit_norm && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && rot_dim % 16 == 0 &&
         row_stride % 8 == 0 && q_stride % 8 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) &&
         !((uintptr_t)k_pages & 15) && !((uintptr_t)v_pages & 15))
         return wllm_launch(rope_kv_write_rows_kernel, n, 128, (size_t)rot_dim * sizeof(float), stream, (const bf16*)qkv, row_stride,
@@ -155,9 +185,10 @@ WLLM_API int wllm_rope_kv_write(const void* qkv, int in_dtype, int row_stride, i
     // 24 us a layer as 256 CTAs and take 6 as 2,560.
     const bool all_heads = n >= 1024;
     const dim3 grid(n, all_heads ? 1 : nq + 2 * nkv);
-#define GO2(TI, TO, A) wllm_launch(rope_kv_write_kernel<TI, TO, A>, grid, threads, 0, stream, (const TI*)qkv, row_stride, in_splits, \
+    const size_t smem = unit_norm ? (size_t)(hd + 32) * sizeof(float) : 0;
+#define GO2(TI, TO, A) wllm_launch(rope_kv_write_kernel<TI, TO, A>, grid, threads, smem, stream, (const TI*)qkv, row_stride, in_splits, \
         (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
-        rot_dim, page_size, interleaved)
+        rot_dim, page_size, interleaved, vd, unit_norm ? 1 : 0, norm_eps)
 #define GO(TI, TO) (all_heads ? GO2(TI, TO, true) : GO2(TI, TO, false))
     if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) return GO(bf16, bf16);
     if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) return GO(float, bf16);
@@ -165,4 +196,13 @@ WLLM_API int wllm_rope_kv_write(const void* qkv, int in_dtype, int row_stride, i
 #undef GO
 #undef GO2
     return WLLM_BAD_DTYPE;
+}
+
+WLLM_API int wllm_rope_kv_write(const void* qkv, int in_dtype, int row_stride, int in_splits, long long in_split_stride,
+                                void* q_out, int out_dtype, int q_stride, const int* positions, const int* slots,
+                                const float* inv_freq, void* k_pages, void* v_pages, int n, int nq, int nkv, int hd,
+                                int rot_dim, int page_size, int interleaved, cudaStream_t stream) {
+    return wllm_rope_kv_write_general(qkv, in_dtype, row_stride, in_splits, in_split_stride, q_out, out_dtype, q_stride,
+                                      positions, slots, inv_freq, k_pages, v_pages, n, nq, nkv, hd, rot_dim, page_size,
+                                      interleaved, hd, 0, 0.f, stream);
 }

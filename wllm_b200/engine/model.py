@@ -35,28 +35,31 @@ class ComposedModel:
                 refs.append(CacheRef(src.group, src.layer, False, src.state_names))
                 continue
             need = self.blocks[run.block].cache_need()
-            if isinstance(need, KVNeed):
-                key = (need.kv_heads, need.head_dim, need.window)
-                if key not in keys:
-                    keys.append(key)
-                    layers.append(0)
-                g = keys.index(key)
-                refs.append(CacheRef(group=g, layer=layers[g]))
-                layers[g] += 1
-            elif isinstance(need, StateNeed):
-                names = {}
-                for name, shape, dt in need.tensors:
-                    names[name] = f"run{i}.{name}"
-                    states.append(StateSpec(names[name], tuple(shape), dt))
-                refs.append(CacheRef(state_names=names))
-            elif need is None:
-                refs.append(CacheRef())
-            else:
-                raise TypeError(f"run {i}: cache_need() returned {need!r}; expected KVNeed, StateNeed or None")
+            ref = CacheRef()
+            for one in need if isinstance(need, (tuple, list)) else (need,):
+                if isinstance(one, KVNeed):
+                    if ref.group is not None:
+                        raise TypeError(f"run {i}: a mixer reads the pages of one cache group")
+                    vd = one.v_head_dim if one.v_head_dim and one.v_head_dim != one.head_dim else None
+                    key = (one.kv_heads, one.head_dim, one.window, vd)
+                    if key not in keys:
+                        keys.append(key)
+                        layers.append(0)
+                    g = keys.index(key)
+                    ref.group, ref.layer = g, layers[g]
+                    layers[g] += 1
+                elif isinstance(one, StateNeed):
+                    ref.state_names = ref.state_names or {}
+                    for name, shape, dt in one.tensors:
+                        ref.state_names[name] = f"run{i}.{name}"
+                        states.append(StateSpec(ref.state_names[name], tuple(shape), dt))
+                elif one is not None:
+                    raise TypeError(f"run {i}: cache_need() returned {one!r}; expected KVNeed, StateNeed, None or a tuple of them")
+            refs.append(ref)
         groups = []
-        for (kvh, hd, window), n in zip(keys, layers):
-            name = ("all" if window is None else f"window{window}") + f"-{kvh}x{hd}"
-            groups.append(CacheGroupSpec(name, n, kvh, hd, window))
+        for (kvh, hd, window, vd), n in zip(keys, layers):
+            name = ("all" if window is None else f"window{window}") + f"-{kvh}x{hd}" + (f"v{vd}" if vd else "")
+            groups.append(CacheGroupSpec(name, n, kvh, hd, window, vd))
         return groups, states, refs
 
     # -- weights -------------------------------------------------------------------
@@ -85,7 +88,10 @@ class ComposedModel:
     def weight_bytes(self) -> int:
         """Bytes of every weight a step reads once (the tied table counts once)."""
         seen, total = set(), 0
-        for part in self.parts():
+        todo = list(self.parts())
+        while todo:
+            part = todo.pop()
+            todo.extend(part.parts() if hasattr(part, "parts") else [])     # a mixer made of mixers
             for t in vars(part).values():
                 if isinstance(t, torch.Tensor) and t.data_ptr() not in seen and t.dim() >= 1 and t.numel() > 1:
                     seen.add(t.data_ptr())

@@ -12,6 +12,7 @@ FAMILIES = {
     "rope_cache": [{}],
     "attention_simt": [{}],
     "activation": [{}],
+    "linear_attention": [{}],
     "gemm_f32": [{}],
     "sampling": [{}],
     "staging": [{}],

@@ -111,9 +111,10 @@ def patch_tokens(ids: torch.Tensor, dst: torch.Tensor, sampled: torch.Tensor, sr
 
 
 def rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, offset: float, out: torch.Tensor,
-            rows=None, delta_splits: int = 0) -> torch.Tensor:
+            rows=None, delta_splits: int = 0, center: bool = False) -> torch.Tensor:
     """Fold `delta` into the residual (when given), then norm: see csrc/norm.cu.  With `delta_splits` = S > 0,
-    `delta` is [S, n, H] float32 partial sums that are added in order."""
+    `delta` is [S, n, H] float32 partial sums that are added in order.  `center`: the row's mean is taken off
+    first (a layer norm without a bias)."""
     _need_cuda(resid, delta, weight, out, rows)
     H = resid.shape[1]
     n = rows.shape[0] if rows is not None else resid.shape[0]
@@ -128,25 +129,58 @@ def rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, offset
         else:
             assert delta.shape == resid.shape
     lib = load_family("norm")
-    _check(lib.wllm_rmsnorm(_ptr(resid), _ptr(delta), _dt(delta) if delta is not None else _F32, max(1, delta_splits),
-                            ctypes.c_longlong(split_stride), _ptr(weight), _dt(weight), c_float(eps), c_float(offset),
-                            _ptr(out), _dt(out), _ptr(_int32(rows, "rows") if rows is not None else None), n, H,
-                            _stream()), "rmsnorm")
+    _check(lib.wllm_norm(_ptr(resid), _ptr(delta), _dt(delta) if delta is not None else _F32, max(1, delta_splits),
+                         ctypes.c_longlong(split_stride), _ptr(weight), _dt(weight), c_float(eps), c_float(offset),
+                         1 if center else 0, _ptr(out), _dt(out), _ptr(_int32(rows, "rows") if rows is not None else None),
+                         n, H, _stream()), "norm")
+    return out
+
+
+def _branch_args(branch, n: int, H: int):
+    """(tensor, parts) of a branch output as the kernels take it: pointer, element type, parts, stride between parts."""
+    t, parts = branch
+    assert t.is_contiguous() and t.shape[-2:] == (n, H)
+    if parts:
+        assert t.dtype == torch.float32 and t.shape[0] == parts
+    return _ptr(t), _dt(t), max(1, parts), ctypes.c_longlong(n * H if parts else 0)
+
+
+def branch_norm(a, weight_a: torch.Tensor, out: torch.Tensor, eps: float, center: bool = False, factor: float = 1.0,
+                b=None, weight_b: torch.Tensor | None = None) -> torch.Tensor:
+    """out[n, H] (float32) = factor * (norm(a) * weight_a [+ norm(b) * weight_b]) for branch outputs that are not part
+    of the residual yet.  `a`, `b`: (tensor [n, H] or float32 partial sums [S, n, H], S or 0), as ops.project returns
+    them.  `center`: layer norm without a bias, else root mean square (csrc/norm.cu)."""
+    n, H = out.shape
+    _need_cuda(a[0], weight_a, out, b[0] if b is not None else None, weight_b)
+    assert out.dtype == torch.float32 and out.is_contiguous() and weight_a.shape == (H,) and weight_a.is_contiguous()
+    pa = _branch_args(a, n, H)
+    if b is not None:
+        assert weight_b is not None and weight_b.shape == (H,) and weight_b.dtype == weight_a.dtype and weight_b.is_contiguous()
+        pb = _branch_args(b, n, H)
+    else:
+        pb = (_ptr(None), _F32, 1, ctypes.c_longlong(0))
+    lib = load_family("norm")
+    _check(lib.wllm_branch_norm(*pa, _ptr(weight_a), *pb, _ptr(weight_b), _dt(weight_a), c_float(eps), 1 if center else 0,
+                                c_float(factor), _ptr(out), n, H, _stream()), "branch_norm")
     return out
 
 
 def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor,
                   k_pages, v_pages, nq: int, nkv: int, hd: int, rot_dim: int, page_size: int, in_splits: int = 0,
-                  pairing: str = "half") -> None:
+                  pairing: str = "half", vd: int | None = None, unit_norm_eps: float | None = None) -> None:
     """Rotate the q and k heads of the fused rows `qkv` [n, (nq+2nkv)*hd] (or [S, n, ...] float32 partial sums
     when in_splits = S > 0); rotated q goes to `q_out` [n, nq*hd], rotated k and v to the pages.
-    pairing 'half': element j turns with j + rot_dim/2; 'interleaved': 2j with 2j + 1."""
+    pairing 'half': element j turns with j + rot_dim/2; 'interleaved': 2j with 2j + 1.
+    `vd`: size of a value head when it is not hd (the row is then nq*hd | nkv*hd | nkv*vd, and may be the first
+    columns of a wider fused row).  `unit_norm_eps`: every rotated q and k head is divided by its root mean
+    square, y / sqrt(mean(y^2) + eps)."""
     if pairing not in ("half", "interleaved"):
         raise KernelError(f"rotary pairing {pairing!r} not supported (half, interleaved)")
     _need_cuda(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages)
-    width = (nq + 2 * nkv) * hd
+    vd = hd if vd is None else vd
+    width = (nq + nkv) * hd + nkv * vd
     if in_splits:
-        assert qkv.dim() == 3 and qkv.shape[0] == in_splits and qkv.is_contiguous() and qkv.dtype == torch.float32
+        assert qkv.dim() == 3 and qkv.shape[0] == in_splits and qkv.stride(2) == 1 and qkv.dtype == torch.float32
         n, row_stride, split_stride = qkv.shape[1], qkv.stride(1), qkv.stride(0)
     else:
         assert qkv.dim() == 2 and qkv.stride(1) == 1
@@ -156,11 +190,12 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tenso
     if slots is not None:
         assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q_out.dtype == v_pages.dtype
     lib = load_family("rope_cache")
-    _check(lib.wllm_rope_kv_write(_ptr(qkv), _dt(qkv), row_stride, max(1, in_splits), ctypes.c_longlong(split_stride),
-                                  _ptr(q_out), _dt(q_out), q_out.stride(0), _ptr(_int32(positions, "positions")),
-                                  _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq),
-                                  _ptr(k_pages), _ptr(v_pages), n, nq, nkv, hd, rot_dim, page_size,
-                                  1 if pairing == "interleaved" else 0, _stream()),
+    _check(lib.wllm_rope_kv_write_general(_ptr(qkv), _dt(qkv), row_stride, max(1, in_splits), ctypes.c_longlong(split_stride),
+                                          _ptr(q_out), _dt(q_out), q_out.stride(0), _ptr(_int32(positions, "positions")),
+                                          _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq),
+                                          _ptr(k_pages), _ptr(v_pages), n, nq, nkv, hd, rot_dim, page_size,
+                                          1 if pairing == "interleaved" else 0, vd, 0 if unit_norm_eps is None else 1,
+                                          c_float(unit_norm_eps or 0.0), _stream()),
            "rope_kv_write")
 
 
@@ -177,25 +212,31 @@ def simt_chunks(max_ctx: int, window: int) -> int:
 def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                          token_req: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                          nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
-                         scratch: torch.Tensor | None = None, max_chunks: int = 0) -> torch.Tensor:
+                         scratch: torch.Tensor | None = None, max_chunks: int = 0, vd: int | None = None,
+                         sinks: torch.Tensor | None = None) -> torch.Tensor:
     """q: [n, nq*hd] view (row stride free); pages: [num_pages, nkv, page_size, hd]; out: [n, nq*hd].
+    `vd`: size of a value head when it is not hd (value pages [.., vd], out [n, nq*vd]); `sinks`: float32 [nq], one
+    more term e^(sink) in every row's softmax denominator.
     With `scratch` (float32, n * nq * max_chunks * (hd + 2) floats) and max_chunks = simt_chunks(...) > 1 every
     (row, chunk of 64 keys) gets a warp of its own and a second kernel merges them; the result is the same,
     bit for bit, as without."""
-    _need_cuda(q, out, k_pages, v_pages, token_req, positions, block_table, scratch)
+    _need_cuda(q, out, k_pages, v_pages, token_req, positions, block_table, scratch, sinks)
     n = q.shape[0]
+    vd = hd if vd is None else vd
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.dim() == 2
+    assert k_pages.shape[-1] == hd and v_pages.shape[-1] == vd
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     if scratch is not None:
         assert scratch.dtype == torch.float32 and scratch.is_contiguous() and max_chunks >= 1
-        assert scratch.numel() >= n * nq * max_chunks * (hd + 2)
+        assert scratch.numel() >= n * nq * max_chunks * (vd + 2)
     lib = load_family("attention_simt")
-    _check(lib.wllm_paged_attention_simt(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
-                                         _dt(q), _ptr(_int32(token_req, "token_req")),
-                                         _ptr(_int32(positions, "positions")), _ptr(_int32(block_table, "block_table")),
-                                         block_table.shape[1], n, nq, nkv, hd, page_size, window, c_float(scale),
-                                         _ptr(scratch), max_chunks if scratch is not None else 0,
-                                         _stream()), f"paged_attention_simt(head_dim={hd}, heads={nq}/{nkv})")
+    _check(lib.wllm_paged_attention_simt_general(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                                 _dt(q), _ptr(_int32(token_req, "token_req")),
+                                                 _ptr(_int32(positions, "positions")), _ptr(_int32(block_table, "block_table")),
+                                                 block_table.shape[1], n, nq, nkv, hd, page_size, window, c_float(scale),
+                                                 _ptr(scratch), max_chunks if scratch is not None else 0, vd, _ptr(sinks),
+                                                 _stream()), f"paged_attention_simt(head_dim={hd}/{vd}, heads={nq}/{nkv})")
     if scratch is not None and max_chunks > 1:
         global launches
         launches += 1    # the merge kernel
@@ -205,20 +246,26 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
 def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                                req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_ctx_len: torch.Tensor,
                                block_table: torch.Tensor, max_q_len: int, nq: int, nkv: int, hd: int, page_size: int,
-                               window: int, scale: float) -> torch.Tensor:
+                               window: int, scale: float, vd: int | None = None,
+                               sinks: torch.Tensor | None = None) -> torch.Tensor:
     """The same attention as `paged_attention_simt`, bit for bit, for steps that bring portions of prompts: a CTA
     takes 32 rows of one (request, key/value head) and reads every tile of keys and values once for all of them
     (csrc/attention_simt.cu, tiled).  Head sizes up to 256; requests are given by their start, length and context."""
-    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table)
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, sinks)
+    vd = hd if vd is None else vd
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.dim() == 2
+    assert k_pages.shape[-1] == hd and v_pages.shape[-1] == vd
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     lib = load_family("attention_simt")
-    _check(lib.wllm_paged_attention_simt_tiled(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
-                                               _dt(q), _ptr(_int32(req_q_start, "req_q_start")),
-                                               _ptr(_int32(req_q_len, "req_q_len")), _ptr(_int32(req_ctx_len, "req_ctx_len")),
-                                               _ptr(_int32(block_table, "block_table")), block_table.shape[1],
-                                               req_q_len.shape[0], max_q_len, nq, nkv, hd, page_size, window, c_float(scale),
-                                               _stream()), f"paged_attention_simt_tiled(head_dim={hd}, heads={nq}/{nkv})")
+    _check(lib.wllm_paged_attention_simt_tiled_general(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages),
+                                                       _ptr(v_pages), _dt(q), _ptr(_int32(req_q_start, "req_q_start")),
+                                                       _ptr(_int32(req_q_len, "req_q_len")),
+                                                       _ptr(_int32(req_ctx_len, "req_ctx_len")),
+                                                       _ptr(_int32(block_table, "block_table")), block_table.shape[1],
+                                                       req_q_len.shape[0], max_q_len, nq, nkv, hd, page_size, window,
+                                                       c_float(scale), vd, _ptr(sinks), _stream()),
+           f"paged_attention_simt_tiled(head_dim={hd}/{vd}, heads={nq}/{nkv})")
     return out
 
 
@@ -357,9 +404,9 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: str) -> torch.Tenso
     _need_cuda(gate_up, out)
     n, two_i = gate_up.shape
     assert gate_up.is_contiguous() and out.is_contiguous() and out.shape == (n, two_i // 2) and out.dtype == gate_up.dtype
-    code = {"gelu_tanh": 0, "silu": 1}.get(act)
+    code = {"gelu_tanh": 0, "silu": 1, "relu": 2}.get(act)
     if code is None:
-        raise KernelError(f"activation {act!r} not supported (gelu_tanh, silu)")
+        raise KernelError(f"activation {act!r} not supported (gelu_tanh, silu, relu)")
     lib = load_family("activation")
     _check(lib.wllm_gated_act(_ptr(gate_up), _ptr(out), _dt(gate_up), code, n, two_i // 2, _stream()), "gated_act")
     return out
@@ -406,7 +453,7 @@ def fma_peak_tflops(device, iters: int = 20000) -> float:
     return best
 
 
-_TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3}
+_TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3, "relu": 4}
 _tc_status: dict = {}
 
 
@@ -495,7 +542,7 @@ def split_plan(M: int, N: int, K: int) -> int:
 def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "bf16",
                  max_ctas: int | None = None, k_splits: int = 1, half_rows: int | None = None, checked: bool = False) -> torch.Tensor:
     """out = a @ w^T on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu).  epilogue 'bf16' | 'f32' (32-bit out) |
-    'gelu_tanh' | 'silu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)).
+    'gelu_tanh' | 'silu' | 'relu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)).
     k_splits > 1 ('f32' only) cuts K into parts; `out` is then [k_splits, M, N] partial sums.
     half_rows: the tile of products of at most 128 rows (see tile_plan, which chooses it when None)."""
     _need_cuda(a, w, out)
@@ -591,8 +638,83 @@ def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.
     return gated_act(gu, out, act)
 
 
+def _fused_args(fused, parts: int):
+    """A fused projection [n, W] (or float32 partial sums [S, n, W]) as the kernels take it."""
+    if parts:
+        assert fused.dim() == 3 and fused.shape[0] == parts and fused.stride(2) == 1 and fused.dtype == torch.float32
+        return _ptr(fused), _dt(fused), fused.stride(1), parts, ctypes.c_longlong(fused.stride(0)), fused.shape[1]
+    assert fused.dim() == 2 and fused.stride(1) == 1
+    return _ptr(fused), _dt(fused), fused.stride(0), 1, ctypes.c_longlong(0), fused.shape[0]
+
+
+def linattn_prepare(fused, parts: int, q_off: int, k_off: int, v_off: int, heads: int, dim: int, vdim: int,
+                    positions: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_scale: float = 1.0,
+                    k_scale: float = 1.0, inv_freq: torch.Tensor | None = None, rot_dim: int = 0, low_off: int = -1,
+                    w2: torch.Tensor | None = None, b2: torch.Tensor | None = None, tau: float = 1.0,
+                    decay: torch.Tensor | None = None) -> None:
+    """The 32-bit inputs of the decayed-state recurrence from a fused projection row (csrc/linear_attention.cu):
+    q [n, heads*dim] and k, turned by the rotary angle of their position over the first rot_dim elements of a head
+    and scaled; v [n, heads*vdim]; and, with `low_off` >= 0, the decay per key channel
+    sigmoid(w2 @ low + b2)^(1/tau), where `low` are the rank = w2.shape[1] columns of the row from `low_off`."""
+    _need_cuda(fused, positions, q, k, v, inv_freq, w2, b2, decay)
+    ptr, dt, row_stride, nparts, part_stride, n = _fused_args(fused, parts)
+    for t, width in ((q, heads * dim), (k, heads * dim), (v, heads * vdim)):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.shape == (n, width)
+    rank = 0
+    if low_off >= 0:
+        rank = w2.shape[1]
+        assert w2.shape == (heads * dim, rank) and w2.is_contiguous() and b2.shape == (heads * dim,) and b2.dtype == w2.dtype
+        assert decay.dtype == torch.float32 and decay.is_contiguous() and decay.shape == (n, heads * dim)
+    if rot_dim:
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2 and inv_freq.is_contiguous()
+    lib = load_family("linear_attention")
+    _check(lib.wllm_linattn_prepare(ptr, dt, row_stride, nparts, part_stride, q_off, k_off, v_off, low_off, n, heads, dim,
+                                    vdim, rank, _ptr(_int32(positions, "positions")), _ptr(inv_freq), rot_dim,
+                                    c_float(q_scale), c_float(k_scale), _ptr(w2), _ptr(b2), _dt(w2) if w2 is not None else _F32,
+                                    c_float(tau), _ptr(q), _ptr(k), _ptr(v), _ptr(decay), _stream()), "linattn_prepare")
+
+
+def linattn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay, head_decay, state: torch.Tensor,
+                 out: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_slot: torch.Tensor, heads: int,
+                 dim: int, vdim: int) -> torch.Tensor:
+    """S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t over every request's tokens of the step, from and to the
+    request's row of `state` [slots, heads, dim, vdim] (float32).  `decay` [n, heads*dim] per key channel, or None
+    with `head_decay` [heads]."""
+    _need_cuda(q, k, v, decay, head_decay, state, out, req_q_start, req_q_len, req_slot)
+    n = q.shape[0]
+    assert all(t.dtype == torch.float32 and t.is_contiguous() for t in (q, k, v, state, out))
+    assert q.shape == k.shape == (n, heads * dim) and v.shape == out.shape == (n, heads * vdim)
+    assert state.shape[1:] == (heads, dim, vdim)
+    if decay is not None:
+        assert decay.dtype == torch.float32 and decay.is_contiguous() and decay.shape == q.shape
+    else:
+        assert head_decay.dtype == torch.float32 and head_decay.shape == (heads,) and head_decay.is_contiguous()
+    lib = load_family("linear_attention")
+    _check(lib.wllm_linattn_scan(_ptr(q), _ptr(k), _ptr(v), _ptr(decay), _ptr(head_decay), _ptr(state), _ptr(out),
+                                 _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
+                                 _ptr(_int32(req_slot, "req_slot")), req_q_len.shape[0], heads, dim, vdim, _stream()),
+           f"linattn_scan(heads={heads}, dim={dim}, vdim={vdim})")
+    return out
+
+
+def head_gate_norm(o: torch.Tensor, fused, parts: int, gate_off: int, weight, eps: float, out: torch.Tensor, heads: int,
+                   vdim: int) -> torch.Tensor:
+    """out[n, heads*vdim] = o / sqrt(mean over a head of o^2 + eps) [* weight[vdim]] * silu(gate), the gate being the
+    columns of the fused projection row from `gate_off`; 32-bit inside, rounded once to out's element type."""
+    _need_cuda(o, fused, weight, out)
+    ptr, dt, row_stride, nparts, part_stride, n = _fused_args(fused, parts)
+    assert o.dtype == torch.float32 and o.is_contiguous() and o.shape == (n, heads * vdim) == out.shape and out.is_contiguous()
+    assert weight is None or (weight.shape == (vdim,) and weight.is_contiguous())
+    lib = load_family("linear_attention")
+    _check(lib.wllm_head_gate_norm(_ptr(o), ptr, dt, row_stride, nparts, part_stride, gate_off, _ptr(weight),
+                                   _dt(weight) if weight is not None else _F32, c_float(eps), _ptr(out), _dt(out), n, heads,
+                                   vdim, _stream()), "head_gate_norm")
+    return out
+
+
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt",
            "paged_attention_simt_tiled",
            "attention_mma_decode", "attention_mma_prefill", "mma_head_dim_ok", "gemm_bf16_tc", "tc_gemm_ok",
            "tc_gemm_status",
-           "gated_act", "gemm_f32", "linear", "project", "gated_linear", "split_plan"]
+           "gated_act", "gemm_f32", "linear", "project", "gated_linear", "split_plan", "branch_norm", "linattn_prepare",
+           "linattn_scan", "head_gate_norm"]

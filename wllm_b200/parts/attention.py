@@ -7,6 +7,16 @@ Query head h reads key/value head h // (num_heads/num_kv_heads); scores are scal
 by head_dim^-0.5 (src/wllm/models/llama.py:74-79, 242).  The three projections are
 stored as one matrix [(nq + 2 nkv) * hd, hidden], rows in the order q, k, v, so one
 product replaces three (the reference runs three, src/wllm/models/llama.py:103-105).
+Further options, all off by default: value_dim (size of a value head when it is not
+head_dim; the output projection then reads num_heads * value_dim columns), scale (the
+score factor in place of head_dim^-0.5), sink (checkpoint name of one number per query
+head that joins the softmax denominator as e^sink, without key or value),
+qk_unit_norm_eps (rotated q and k heads are divided by their root mean square,
+y / sqrt(mean(y^2) + eps), before the scores).
+
+A mixer may be one of several that read the same input (a block that runs two mixers side
+by side): `input_weights()` lists the matrices that read the input, `mix(fused, parts,
+col0, ...)` runs the mixer on its columns of a fused product that somebody else made.
 
 One forward serves whole prompts, portions and decoded tokens alike: the step's keys
 and values go into the pages first, then every token attends through its request's
@@ -37,55 +47,84 @@ class PagedAttention:
         self.hidden_size, self.model_dtype = hidden_size, model_dtype
         self.names = {k: spec.options[k] for k in ("q_proj", "k_proj", "v_proj", "o_proj")}
         self.position = POSITIONS.build(spec.position)
-        self.scale = float(self.hd) ** -0.5
-        self.wqkv = self.wo = None
+        self.vd = int(spec.options.get("value_dim") or self.hd)
+        if self.vd % 8 or self.hd % 8:
+            raise ValueError(f"head sizes {self.hd} / {self.vd}: the attention kernels read heads in steps of 8 elements")
+        scale = spec.options.get("scale")
+        self.scale = float(self.hd) ** -0.5 if scale is None else float(scale)
+        self.sink_name = spec.options.get("sink")
+        self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
+        # the tensor-core kernels take equal head sizes and a plain softmax; everything else runs on the general ones
+        self.general = self.vd != self.hd or self.sink_name is not None
+        self.width = (self.nq + self.nkv) * self.hd + self.nkv * self.vd      # columns of the fused q|k|v row
+        self.tag = ""                    # set by a mixer that runs this one beside another: keeps their buffers apart
+        self.wqkv = self.wo = self.sinks = None
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.hd, self.window)
+        return KVNeed(self.nkv, self.hd, self.window, self.vd if self.vd != self.hd else None)
 
     def param_specs(self):
         H, n = self.hidden_size, self.names
-        return [ParamSpec(n["q_proj"], (self.nq * self.hd, H)), ParamSpec(n["k_proj"], (self.nkv * self.hd, H)),
-                ParamSpec(n["v_proj"], (self.nkv * self.hd, H)), ParamSpec(n["o_proj"], (H, self.nq * self.hd))]
+        out = [ParamSpec(n["q_proj"], (self.nq * self.hd, H)), ParamSpec(n["k_proj"], (self.nkv * self.hd, H)),
+               ParamSpec(n["v_proj"], (self.nkv * self.vd, H)), ParamSpec(n["o_proj"], (H, self.nq * self.vd))]
+        if self.sink_name is not None:
+            out.append(ParamSpec(self.sink_name, (self.nq,), "vector"))
+        return out
 
     def load(self, fetch):
         n = self.names
         self.wqkv = torch.cat([fetch(n["q_proj"]), fetch(n["k_proj"]), fetch(n["v_proj"])], dim=0).contiguous()
         self.wo = fetch(n["o_proj"]).contiguous()
+        if self.sink_name is not None:
+            self.sinks = fetch(self.sink_name).to(torch.float32).contiguous()
         self.position.to(self.wo.device)
 
+    def input_weights(self) -> list:
+        return [self.wqkv]
+
     def __call__(self, x: torch.Tensor, ctx, cache: CacheRef):
-        n = x.shape[0]
-        qkv, parts = ops.project(x, self.wqkv, lambda name, shape, dt: ctx.buffer("qkv_" + name, shape, dt))
+        qkv, parts = ops.project(x, self.wqkv, lambda name, shape, dt: ctx.buffer(self.tag + "qkv_" + name, shape, dt))
+        return self.mix(qkv, parts, 0, ctx, cache)
+
+    def mix(self, fused: torch.Tensor, parts: int, col0: int, ctx, cache: CacheRef):
+        """The mixer on columns col0 .. col0 + width of a fused product [n, W] (or partial sums [parts, n, W])."""
+        n = fused.shape[-2]
+        qkv = fused if fused.shape[-1] == self.width else fused[..., col0:col0 + self.width]
         group = ctx.cache.groups[cache.group]
         k_pages, v_pages = group.keys(cache.layer), group.values(cache.layer)
-        q = ctx.buffer("q_rotated", (n, self.nq * self.hd), self.model_dtype)
+        q = ctx.buffer(self.tag + "q_rotated", (n, self.nq * self.hd), self.model_dtype)
+        extra = {}
+        if self.vd != self.hd:
+            extra["vd"] = self.vd
+        if self.unit_norm_eps is not None:
+            extra["unit_norm_eps"] = float(self.unit_norm_eps)
         ops.rope_kv_write(qkv, q, ctx.positions, ctx.group_slots[cache.group] if cache.writes else None,
                           self.position.inv_freq, k_pages, v_pages, self.nq, self.nkv, self.hd,
                           self.position.rotary_dim, group.page_size, in_splits=parts,
-                          pairing=getattr(self.position, "pairing", "half"))
-        attn = ctx.buffer("attn", (n, self.nq * self.hd), self.model_dtype)
+                          pairing=getattr(self.position, "pairing", "half"), **extra)
+        attn = ctx.buffer(self.tag + "attn", (n, self.nq * self.vd), self.model_dtype)
         self.attend(q, attn, k_pages, v_pages, ctx, cache.group)
-        return as_branch(ops.project(attn, self.wo, lambda name, shape, dt: ctx.buffer("branch_" + name, shape, dt)))
+        return as_branch(ops.project(attn, self.wo, lambda name, shape, dt: ctx.buffer(self.tag + "branch_" + name, shape, dt)))
 
     def attend(self, q, out, k_pages, v_pages, ctx, group: int) -> None:
         """Attention of every token of the step over its request's pages of cache group `group`."""
         nq, nkv, hd, window, scale = self.nq, self.nkv, self.hd, self.window or 0, self.scale
         ps, table = ctx.cache.page_size, ctx.group_tables[group]
-        if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd):
+        if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd) or self.general:
             # Three kernels with one result, bit for bit, so the choice is one of speed alone.  Portions of prompts:
             # 32 rows of a request share every tile of keys.  Few rows over long contexts (decoding): a warp per
             # (row, chunk of 64 keys).  Otherwise a warp per row.
-            if ctx.num_multi > 0 and hd <= 256:
+            extra = {"vd": self.vd, "sinks": self.sinks} if self.general else {}
+            if ctx.num_multi > 0 and hd <= 256 and self.vd <= 256:
                 ops.paged_attention_simt_tiled(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len,
-                                               table, ctx.max_q_len, nq, nkv, hd, ps, window, scale)
+                                               table, ctx.max_q_len, nq, nkv, hd, ps, window, scale, **extra)
                 return
             rows, chunks = q.shape[0] * nq, ops.simt_chunks(ctx.max_ctx, window)
             scratch = None
             if chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
-                scratch = ctx.buffer("attention_chunks", (rows * chunks * (hd + 2),), torch.float32)
+                scratch = ctx.buffer(self.tag + "attention_chunks", (rows * chunks * (self.vd + 2),), torch.float32)
             ops.paged_attention_simt(q, out, k_pages, v_pages, ctx.token_req, ctx.positions, table, nq, nkv, hd, ps,
-                                     window, scale, scratch, chunks)
+                                     window, scale, scratch, chunks, **extra)
             return
         decode = ctx.num_single > 0 and nq // nkv <= 16
         if decode:

@@ -20,7 +20,8 @@ Interfaces (duck-typed; see the built-in parts for examples):
                     rows(residual, rows, ctx) -> the same at selected rows only
     position        an object the mixer of its kind understands (rotary: .inv_freq, .rotary_dim, and
                     optionally .pairing = 'half' | 'interleaved')
-    mixer           cache_need() -> KVNeed | StateNeed | None
+    mixer           cache_need() -> KVNeed | StateNeed | None, or a tuple of them (a mixer that reads pages
+                    and keeps state of its own)
                     __call__(x, ctx, cache: CacheRef) -> tensor [n, hidden]
     feed-forward    __call__(x, ctx) -> tensor [n, hidden]
     block           __call__(residual, ctx, cache: CacheRef) -> None (updates the residual)
@@ -73,6 +74,7 @@ class KVNeed:
     kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None    # size of a value head when it differs from head_dim
 
 
 @dataclass(frozen=True)

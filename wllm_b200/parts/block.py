@@ -6,6 +6,13 @@ A branch's output is left pending on the residual and folded in by the next norm
 (the next block's, or the model's final one).
 
 spec options: norm_in, mixer, norm_post, feed_forward (specs).
+
+'sandwich': a norm in front of and behind each sublayer,
+    x = x + norm_mixer_out(mixer(norm_in(x)));  x = x + norm_ff_out(feed_forward(norm_post(x)))
+The norm behind a sublayer acts on the branch alone (`norm.branch`); its 32-bit result is what the next norm folds
+into the residual.  `feed_forward` may be None: the block then has its first sublayer only.
+
+spec options: norm_in, mixer, norm_mixer_out, and norm_post, feed_forward, norm_ff_out (all three or none).
 """
 from __future__ import annotations
 
@@ -31,3 +38,31 @@ class PreNormBlock:
     def __call__(self, residual: Residual, ctx, cache: CacheRef) -> None:
         residual.pending = self.mixer(self.norm_in(residual, ctx), ctx, cache)
         residual.pending = self.feed_forward(self.norm_post(residual, ctx), ctx)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock:
+    graph_safe = True
+
+    def __init__(self, spec, hidden_size: int, model_dtype):
+        kw = dict(hidden_size=hidden_size, model_dtype=model_dtype)
+        self.norm_in = NORMS.build(spec.norm_in, **kw)
+        self.mixer = MIXERS.build(spec.mixer, **kw)
+        self.norm_mixer_out = NORMS.build(spec.norm_mixer_out, **kw)
+        self.feed_forward = None
+        if spec.options.get("feed_forward") is not None:
+            self.norm_post = NORMS.build(spec.norm_post, **kw)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, **kw)
+            self.norm_ff_out = NORMS.build(spec.norm_ff_out, **kw)
+
+    def parts(self):
+        first = [self.norm_in, self.mixer, self.norm_mixer_out]
+        return first if self.feed_forward is None else first + [self.norm_post, self.feed_forward, self.norm_ff_out]
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def __call__(self, residual: Residual, ctx, cache: CacheRef) -> None:
+        residual.pending = self.norm_mixer_out.branch(self.mixer(self.norm_in(residual, ctx), ctx, cache), ctx, "mixer_normed")
+        if self.feed_forward is not None:
+            residual.pending = self.norm_ff_out.branch(self.feed_forward(self.norm_post(residual, ctx), ctx), ctx, "ff_normed")

@@ -1,7 +1,7 @@
 """Gated dense feed-forward: down(act(gate(x)) * up(x)).
 
 spec options: intermediate_size, activation ('gelu_tanh' for Gemma's GeGLU,
-src/wllm/models/gemma.py:54-62; 'silu'), gate_proj/up_proj/down_proj (checkpoint
+src/wllm/models/gemma.py:54-62; 'silu'; 'relu'), gate_proj/up_proj/down_proj (checkpoint
 names).  gate and up are stored as one matrix [2 I, hidden] (gate rows first).  Under
 bfloat16 one tensor-memory GEMM computes both products and applies act(gate) * up in its
 epilogue, in 32-bit on the accumulators; otherwise one product feeds the activation kernel.
@@ -20,6 +20,8 @@ class GatedDense:
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.inter = int(spec.intermediate_size)
         self.activation = spec.activation
+        if self.activation not in ("gelu_tanh", "silu", "relu"):
+            raise ValueError(f"activation {self.activation!r}: gelu_tanh, silu or relu")
         self.hidden_size, self.model_dtype = hidden_size, model_dtype
         self.names = {k: spec.options[k] for k in ("gate_proj", "up_proj", "down_proj")}
         self.wgu = self.wd = None

@@ -1,25 +1,30 @@
-"""Root-mean-square norm with the residual add folded in.
+"""Norms over the model width with the residual add folded in.
 
-spec options: weight (checkpoint name), eps, unit_offset (True: gain is 1 + w, as
-Gemma stores it, src/wllm/models/gemma.py:42-51; False: gain is w).
-The statistics and the gain are applied in 32-bit on the 32-bit residual; the
-result is rounded once to the model's element type.
+'rmsnorm'    x / sqrt(mean(x^2) + eps) * gain.  spec options: weight (checkpoint name), eps, unit_offset (True: gain is
+             1 + w, as Gemma stores it, src/wllm/models/gemma.py:42-51; False: gain is w).
+'layernorm'  (x - mean(x)) / sqrt(mean((x - mean)^2) + eps) * w, a layer norm with a gain and no bias.
+             spec options: weight, eps.
+The statistics and the gain are applied in 32-bit on the 32-bit residual; the result is rounded once to the model's
+element type.  `branch` norms a sublayer's output that has not joined the residual yet (blocks that norm behind
+their sublayers as well as in front): its result stays 32-bit and becomes the residual's pending addend.
 """
 from __future__ import annotations
 
 import torch
 
 from ..kernels import ops
-from .base import NORMS, ParamSpec, Residual
+from .base import NORMS, ParamSpec, Partials, Residual
 
 
 @NORMS.register("rmsnorm")
 class RMSNorm:
     graph_safe = True
+    center = False
+
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.weight_name = spec.weight
         self.eps = float(spec.eps)
-        self.offset = 1.0 if spec.unit_offset else 0.0
+        self.offset = 1.0 if spec.options.get("unit_offset", False) else 0.0
         self.hidden_size = hidden_size
         self.model_dtype = model_dtype
         self.weight = None
@@ -33,12 +38,32 @@ class RMSNorm:
     def __call__(self, residual: Residual, ctx) -> torch.Tensor:
         out = ctx.buffer("normed", (residual.stream.shape[0], self.hidden_size), self.model_dtype)
         delta, parts = residual.pending_args()
-        ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, delta_splits=parts)
+        if self.center:
+            ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, delta_splits=parts, center=True)
+        else:
+            ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, delta_splits=parts)
         residual.pending = None
         return out
 
     def rows(self, residual: Residual, rows: torch.Tensor, ctx) -> torch.Tensor:
         out = torch.empty((rows.shape[0], self.hidden_size), dtype=self.model_dtype, device=rows.device)
         delta, parts = residual.pending_args()
-        ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, rows=rows, delta_splits=parts)
+        if self.center:
+            ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, rows=rows, delta_splits=parts,
+                        center=True)
+        else:
+            ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, rows=rows, delta_splits=parts)
         return out
+
+    def branch(self, branch, ctx, name: str = "branch_normed") -> torch.Tensor:
+        """The norm of a branch output (a tensor [n, hidden] or `Partials`), 32-bit; a gain of 1 + w is not offered here."""
+        if self.offset:
+            raise ValueError("the norm of a branch takes its gain as stored (unit_offset is for norms of the residual)")
+        pair = (branch.tensor, branch.parts) if isinstance(branch, Partials) else (branch, 0)
+        out = ctx.buffer(name, (pair[0].shape[-2], self.hidden_size), torch.float32)
+        return ops.branch_norm(pair, self.weight, out, self.eps, center=self.center)
+
+
+@NORMS.register("layernorm")
+class LayerNormNoBias(RMSNorm):
+    center = True

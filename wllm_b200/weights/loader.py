@@ -3,7 +3,8 @@
 The model says which tensors it reads (name, shape, kind); the folder's
 `*.safetensors` files say which they hold.  Before anything is copied the two lists
 are compared, and one `WeightError` names every missing tensor, every unexpected
-one and every wrong shape.  The reference raises on missing and unexpected names
+one and every wrong shape (a size that the model leaves open, None in its list, is taken
+from the file).  The reference raises on missing and unexpected names
 after loading everything into host memory (src/wllm/models/llama.py:640-649); here
 tensors are read one at a time and go straight to the device.
 
@@ -49,7 +50,8 @@ def check_names(expected: list, where: dict, folder: str) -> None:
     for name, ps in want.items():
         if name in where:
             shape = tuple(where[name].get_slice(name).get_shape())
-            if shape != tuple(ps.shape):
+            # a size the model leaves open (None) is read from the file; the part checks it against its other tensors
+            if len(shape) != len(ps.shape) or any(want is not None and want != got for want, got in zip(ps.shape, shape)):
                 wrong.append(f"{name}: expected {tuple(ps.shape)}, file has {shape}")
     if missing or unexpected or wrong:
         lines = [f"{folder}: the checkpoint does not match the model"]

@@ -15,13 +15,13 @@ import os
 import torch
 from safetensors.torch import save_file
 
-from ..config.registry import resolve_architecture
+from ..config.registry import named_architectures, resolve_architecture
 
 
 def _typed(config):
     """(architecture entry, typed configuration) from a typed configuration or a raw dictionary."""
     if isinstance(config, dict):
-        arch = resolve_architecture(config.get("architectures") or [])
+        arch = resolve_architecture(named_architectures(config))
         return arch, arch.config_class.from_dict(config, where="configuration")
     return resolve_architecture(config.architecture), config
 
@@ -33,6 +33,9 @@ def random_tensors(config, seed: int, dtype=torch.bfloat16, std: float = 0.02, v
     g = torch.Generator().manual_seed(seed)
     out = {}
     for ps in model.param_specs():
+        if any(d is None for d in ps.shape):
+            raise ValueError(f"tensor {ps.name}: shape {ps.shape} has a size that only a checkpoint gives; random weights "
+                             f"need it in the configuration")
         s = vector_std if ps.kind == "vector" else std
         out[ps.name] = (torch.randn(tuple(ps.shape), generator=g, dtype=torch.float32) * s).to(dtype)
     return out
