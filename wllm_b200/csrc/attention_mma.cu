@@ -365,7 +365,8 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
               const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
               const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
               const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
-              int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status) {
+              int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status,
+              const float* __restrict__ sinks) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     const int split = blockIdx.z, g = blockIdx.y, r = blockIdx.x;     // CTAs start request by request, the last (shortest) splits last
@@ -450,6 +451,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
         }
         const int head = g * rep + row;
         if (num_splits == 1) {
+            if (sinks) L += exp2f(sinks[head] * LOG2E - mbase);      // the sink: one more term of the denominator
             out[(size_t)token * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O / L);
         } else {
             const size_t slot = ((size_t)r * nq + head) * max_splits + split;
@@ -488,7 +490,7 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
                  const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                  const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
                  int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                 int whole_rows, int* __restrict__ status) {
+                 int whole_rows, int* __restrict__ status, const float* __restrict__ sinks) {
     extern __shared__ unsigned char smem_raw[];
     pdl_launch_dependents();
     // The step's index arrays were copied before its first kernel started, and no kernel of this step writes
@@ -661,7 +663,8 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
         }
         const int head = g * rep + row;
         if (num_splits == 1) {
-            const float L = sm_row[row * 2 + 1];
+            float L = sm_row[row * 2 + 1];
+            if (sinks) L += exp2f(sinks[head] * LOG2E - (sm_row[row * 2] == -INFINITY ? 0.f : sm_row[row * 2]));
             __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + (size_t)token * out_stride + (size_t)head * HD + d);
             dst[0] = __floats2bfloat162_rn(O.x / L, O.y / L);
             dst[1] = __floats2bfloat162_rn(O.z / L, O.w / L);
@@ -682,7 +685,7 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
 __global__ void merge_kernel(bf16* __restrict__ out, int out_stride, const int* __restrict__ req_q_start,
                              const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len, int nq,
                              int split_keys, int max_splits, const float* __restrict__ part_o,
-                             const float* __restrict__ part_ml) {
+                             const float* __restrict__ part_ml, const float* __restrict__ sinks) {
     pdl_begin();
     const int head = blockIdx.x, r = blockIdx.y;
     if (req_q_len[r] != 1) return;
@@ -710,6 +713,7 @@ __global__ void merge_kernel(bf16* __restrict__ out, int out_stride, const int* 
             for (int u = 0; u < 32; ++u) O += p[u] * __shfl_sync(0xffffffffu, w, u);     // a split past the end has p = 0
             M = M_new;
         }
+        if (sinks) L += exp2f(sinks[head] * LOG2E - (M == -INFINITY ? 0.f : M));
         if (live) out[(size_t)req_q_start[r] * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O / L);
     }
 }
@@ -729,7 +733,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
-               int skip_single, int* __restrict__ status) {
+               int skip_single, int* __restrict__ status, const float* __restrict__ sinks) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     const int g = blockIdx.x, r = blockIdx.y;                 // grid (key/value heads, requests, tiles): the longest tiles start first
@@ -796,7 +800,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     for (int i = 0; i < 2; ++i) {
         const int m = row0 + warp * 16 + (lane >> 2) + i * 8;
         if (m >= rows) continue;
-        const float inv = 1.0f / st.l[i];
+        const float inv = 1.0f / (sinks ? st.l[i] + exp2f(sinks[g * rep + m % rep] * LOG2E - st.m[i]) : st.l[i]);
         bf16* dst = out + (size_t)(q_start + m / rep) * out_stride + (size_t)(g * rep + m % rep) * HD + (lane & 3) * 2;
 #pragma unroll
         for (int n = 0; n < NTO; ++n) {
@@ -902,12 +906,13 @@ static int check_common(const void* q, int q_stride, const void* out, int out_st
 // Tokens of requests with q_len == 1.  `scratch` holds wllm_attention_mma_scratch_floats(...) floats;
 // `pool_pages` is the number of pages of k_pages / v_pages; `status` is a device int that stays 0 unless
 // a CTA gave up waiting for a tile.
-WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                       const void* v_pages, long long pool_pages, const int* req_q_start,
-                                       const int* req_q_len, const int* req_ctx_len, const int* block_table,
-                                       int max_pages, int requests, int nq, int nkv, int page_size, int window,
-                                       float scale, int split_keys, int max_splits, float* scratch, int* status,
-                                       cudaStream_t stream) {
+// `sinks` (null: none): one 32-bit number per query head, one more term e^sink of every row's softmax denominator.
+WLLM_API int wllm_attention_mma_decode_sinks(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                             const void* v_pages, long long pool_pages, const int* req_q_start,
+                                             const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                             int max_pages, int requests, int nq, int nkv, int page_size, int window,
+                                             float scale, int split_keys, int max_splits, float* scratch, int* status,
+                                             const float* sinks, cudaStream_t stream) {
     if (requests <= 0) return WLLM_OK;
     const int bad = check_common(q, q_stride, out, out_stride, k_pages, v_pages, nq, nkv, page_size, pool_pages);
     if (bad) return bad;
@@ -939,16 +944,27 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
         st = wllm_launch(decode_ws_kernel, dim3(requests, nkv, max_splits), WS_THREADS, WS_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                          block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys, max_splits, part_o,
-                         part_ml, whole_rows ? 1 : 0, status);
+                         part_ml, whole_rows ? 1 : 0, status, sinks);
     else
         st = wllm_launch(decode_kernel, dim3(requests, nkv, max_splits), NTHREADS, DEC_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                          req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window,
-                         scale * LOG2E, split_keys, max_splits, part_o, part_ml, status);
+                         scale * LOG2E, split_keys, max_splits, part_o, part_ml, status, sinks);
     if (st || max_splits == 1) return st;
     return wllm_launch(merge_kernel, dim3(nq, requests), HD >= 256 ? 256 : (HD >= 128 ? 128 : 64), 0, stream,
                        (bf16*)out, out_stride, req_q_start, req_q_len, req_ctx_len, nq, split_keys, max_splits,
-                       (const float*)part_o, (const float*)part_ml);
+                       (const float*)part_o, (const float*)part_ml, sinks);
+}
+
+WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                       const void* v_pages, long long pool_pages, const int* req_q_start,
+                                       const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                       int max_pages, int requests, int nq, int nkv, int page_size, int window,
+                                       float scale, int split_keys, int max_splits, float* scratch, int* status,
+                                       cudaStream_t stream) {
+    return wllm_attention_mma_decode_sinks(q, q_stride, out, out_stride, k_pages, v_pages, pool_pages, req_q_start, req_q_len,
+                                           req_ctx_len, block_table, max_pages, requests, nq, nkv, page_size, window, scale,
+                                           split_keys, max_splits, scratch, status, nullptr, stream);
 }
 
 // Floats of `halves` for a prefill launch that shares tiles between two CTAs.
@@ -958,12 +974,12 @@ WLLM_API long long wllm_attention_mma_prefill_halves_floats(int requests, int ma
 }
 
 // Tokens of requests with q_len > 1 (and of those with q_len == 1 too unless skip_single).
-WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                        const void* v_pages, long long pool_pages, const int* req_q_start,
-                                        const int* req_q_len, const int* req_ctx_len, const int* block_table,
-                                        int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
-                                        int window, float scale, int skip_single, int split_above, float* halves,
-                                        int* status, cudaStream_t stream) {
+WLLM_API int wllm_attention_mma_prefill_sinks(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                              const void* v_pages, long long pool_pages, const int* req_q_start,
+                                              const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                              int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
+                                              int window, float scale, int skip_single, int split_above, float* halves,
+                                              int* status, const float* sinks, cudaStream_t stream) {
     // split_above > 0 (tensor-memory kernel only): a tile of 128 rows that walks more than split_above tiles of
     // 64 keys is shared by two CTAs; `halves` then holds wllm_attention_mma_prefill_halves_floats(...) floats.
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
@@ -1008,7 +1024,7 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
         const int pair_tiles = (max_q_len * (nq / nkv) + 2 * TC_BM - 1) / (2 * TC_BM);
         return wllm_launch(prefill_pair_kernel, dim3(2 * nkv, requests, pair_tiles), TC_THREADS, PR_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
-                           block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status);
+                           block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status, sinks);
     }
 #endif
     if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
@@ -1021,11 +1037,22 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
         return wllm_launch(prefill_tc_kernel, dim3(nkv, requests, split_above > 0 ? 2 * tiles : tiles), TC_THREADS, TC_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                            block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, split_above, halves,
-                           arrivals, status);
+                           arrivals, status, sinks);
     }
 #endif
     return wllm_launch(prefill_kernel, dim3(nkv, requests, tiles), PRE_THREADS, PRE_SMEM, stream,
                        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                        req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E,
-                       skip_single, status);
+                       skip_single, status, sinks);
+}
+
+WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                        const void* v_pages, long long pool_pages, const int* req_q_start,
+                                        const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                        int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
+                                        int window, float scale, int skip_single, int split_above, float* halves,
+                                        int* status, cudaStream_t stream) {
+    return wllm_attention_mma_prefill_sinks(q, q_stride, out, out_stride, k_pages, v_pages, pool_pages, req_q_start, req_q_len,
+                                            req_ctx_len, block_table, max_pages, requests, max_q_len, nq, nkv, page_size,
+                                            window, scale, skip_single, split_above, halves, status, nullptr, stream);
 }

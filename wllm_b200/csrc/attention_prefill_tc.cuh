@@ -50,7 +50,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                   const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                   const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
                   int skip_single, int split_above, float* __restrict__ halves, int* __restrict__ arrivals,
-                  int* __restrict__ status) {
+                  int* __restrict__ status, const float* __restrict__ sinks) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ int s_second;
     pdl_begin();
@@ -290,6 +290,8 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         if (ok && !mbar_wait(pv_done, (T - 1) & 1)) ok = false;
         ok = __all_sync(0xffffffffu, ok);        // the tensor-memory loads below are collective: all lanes or none
         bf16* dst = m_row < rows ? out + (size_t)(q_start + m_row / rep) * out_stride + (size_t)(g * rep + m_row % rep) * HD : nullptr;
+        // the row's sink in the scores' base-2 scale; without one the term below is 2^(-inf) = 0 and changes no bit
+        const float sink2 = (sinks && m_row < rows) ? sinks[g * rep + m_row % rep] * LOG2E : -INFINITY;
         if (shared_tile) {
             // Two CTAs hold halves of this tile's keys.  Each writes its half result (unnormalised O, reference
             // maximum, sum) and counts itself in; the one that comes second adds the other's to its own, which
@@ -327,7 +329,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                 const float m_b = __ldcg(other + (size_t)HD * TC_BM + row * 2), l_b = __ldcg(other + (size_t)HD * TC_BM + row * 2 + 1);
                 const float M = fmaxf(m_run, m_b), mb = M == -INFINITY ? 0.f : M;
                 const float fa = exp2f(m_run - mb), fb = exp2f(m_b - mb);
-                const float inv = 1.0f / __fadd_rn(__fmul_rn(l_run, fa), __fmul_rn(l_b, fb));
+                const float inv = 1.0f / __fadd_rn(__fadd_rn(__fmul_rn(l_run, fa), __fmul_rn(l_b, fb)), exp2f(sink2 - mb));
 #pragma unroll 1
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t ov[32];
@@ -354,7 +356,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             if (!ok && lane == 0) atomicExch(status, GAVE_UP_TC_SOFTMAX);
         } else if (ok) {
             tc_fence_after();
-            const float inv = 1.0f / l_run;
+            const float inv = 1.0f / (l_run + exp2f(sink2 - m_run));
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t ov[32];
@@ -414,7 +416,7 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                     const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
-                    int skip_single, int* __restrict__ status) {
+                    int skip_single, int* __restrict__ status, const float* __restrict__ sinks) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     // grid (2 x key/value heads, requests, tiles): the pairs start in the order x, y, z, the tiles that walk the most
@@ -639,7 +641,8 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
         ok = __all_sync(0xffffffffu, ok);        // the tensor-memory loads below are collective: all lanes or none
         if (ok) {
             tc_fence_after();
-            const float inv = 1.0f / l_run;
+            const float sink2 = (sinks && m_row < rows) ? sinks[g * rep + m_row % rep] * LOG2E : -INFINITY;
+            const float inv = 1.0f / (l_run + exp2f(sink2 - m_run));      // no sink: 2^(-inf) = 0 changes no bit
             bf16* dst = m_row < rows ? out + (size_t)(q_start + m_row / rep) * out_stride + (size_t)(g * rep + m_row % rep) * HD : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {

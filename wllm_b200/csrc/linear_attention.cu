@@ -16,7 +16,9 @@
 //   wllm_linattn_scan       the recurrence.  Grid (tiles of 32 value columns, heads, requests); a lane owns one
 //                           column of S, a warp a run of at most 16 key channels of it, in registers.  Tokens
 //                           arrive in tiles of 8 through a two-stage cp.async ring; the warps' partial dot products of a
-//                           token meet in shared memory and are added in warp order.
+//                           token meet in shared memory and are added in warp order.  Long portions of prompts are cut
+//                           into segments that are walked side by side: from zero for their local end states, which a
+//                           small kernel chains into start states, and once more from those for the outputs.
 //   wllm_head_gate_norm     per head: o / sqrt(mean(o^2) + eps) [* w] * silu(g), rounded once to the matrix type
 //                           (the operand of the output projection).
 #include "common.cuh"
@@ -108,18 +110,31 @@ __device__ __forceinline__ void la_cp4(float* smem_dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
 
-template <bool PER_CHANNEL>
+// MODE 0  a request's tokens of the step in one walk: from its state slot, outputs written, back to the slot.
+// Long portions are cut into segments of `seg_len` tokens that are walked at the same time (grid z = request * max_seg + segment):
+// MODE 1  every segment but a request's last, from a zero state and without outputs: its local end state L and the
+//         product A of its decays per key channel go to scratch[(request * max_seg + segment + 1)] (the place of the
+//         next segment's start).  linattn_combine_kernel then turns them into start states in segment order:
+//         start_(j+1) = diag(A_j) start_j + L_j, start_0 = the slot's state (copied beside them).
+// MODE 2  every segment again, from its start state, with outputs; the last one leaves the request's new state.
+// The state that a token meets is the same up to rounding in all modes; the arithmetic from there is the same.
+template <bool PER_CHANNEL, int MODE>
 __global__ void __launch_bounds__(1024)
 linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                     const float* __restrict__ decay, const float* __restrict__ head_decay, float* __restrict__ state,
                     float* __restrict__ out, const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
-                    const int* __restrict__ req_slot, int H, int D, int V, int cpt) {
+                    const int* __restrict__ req_slot, int H, int D, int V, int cpt, int seg_len, int max_seg,
+                    float* __restrict__ seg_state, float* __restrict__ seg_decay) {
     extern __shared__ float la_smem[];
     pdl_begin();
-    const int r = blockIdx.z, h = blockIdx.y;
-    const int q_len = req_q_len[r], slot = req_slot[r];
-    if (q_len <= 0 || slot < 0) return;                       // a request that brings no token
-    const int t0 = req_q_start[r];
+    const int r = MODE == 0 ? blockIdx.z : blockIdx.z / max_seg, seg = MODE == 0 ? 0 : blockIdx.z % max_seg, h = blockIdx.y;
+    const int req_len = req_q_len[r], slot = req_slot[r];
+    if (req_len <= 0 || slot < 0) return;                     // a request that brings no token
+    const int nseg = MODE == 0 ? 1 : (req_len + seg_len - 1) / seg_len;
+    if (seg >= nseg || (MODE == 1 && seg == nseg - 1)) return;
+    const int tok_lo = MODE == 0 ? 0 : seg * seg_len;
+    const int q_len = MODE == 0 ? req_len : min(req_len - tok_lo, seg_len);      // tokens of this walk
+    const int t0 = req_q_start[r] + tok_lo;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int j = blockIdx.x * LA_COLS + lane;                // this lane's column of S
     const bool col = j < V;
@@ -129,10 +144,16 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
     float* stage0 = la_smem;
     float* red = la_smem + 2 * LA_TT * per_token;             // [2][warps][32]
 
-    float S[LA_CPT];
+    float S[LA_CPT], P[LA_CPT];
     float* Sg = state + (((size_t)slot * H + h) * D) * V;
+    // (a request of several segments reads every start from the scratch, the first one too: its last segment
+    // may write the slot before its first one has started)
+    const float* S0 = (MODE == 2 && nseg > 1) ? seg_state + (((size_t)(r * max_seg + seg) * H + h) * D) * V : Sg;
 #pragma unroll
-    for (int i = 0; i < LA_CPT; ++i) S[i] = (col && c_lo + i < c_hi) ? Sg[(size_t)(c_lo + i) * V + j] : 0.f;
+    for (int i = 0; i < LA_CPT; ++i) {
+        S[i] = (MODE != 1 && col && c_lo + i < c_hi) ? S0[(size_t)(c_lo + i) * V + j] : 0.f;
+        P[i] = 1.f;
+    }
     const float fixed = PER_CHANNEL ? 0.f : head_decay[h];
 
     auto load_tile = [&](int tile, int stage) {
@@ -179,9 +200,11 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
                 if (c_lo + i < c_hi) {
                     const float a = PER_CHANNEL ? as[c_lo + i] : fixed;
                     S[i] = fmaf(a, S[i], ks[c_lo + i] * vj);
-                    partial = fmaf(S[i], qs[c_lo + i], partial);
+                    if (MODE == 1) P[i] *= a;
+                    else partial = fmaf(S[i], qs[c_lo + i], partial);
                 }
             }
+            if (MODE == 1) continue;
             red[(round * warps + warp) * 32 + lane] = partial;
             __syncthreads();
             if (warp == 0 && col) {
@@ -191,38 +214,88 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
             }
             round ^= 1;
         }
+        if (MODE == 1) __syncthreads();       // the stage is read to its end before the tile after next lands in it
     }
-    if (col) {
+    if (MODE == 1) {
+        float* Ld = seg_state + (((size_t)(r * max_seg + seg + 1) * H + h) * D) * V;
+        float* Ad = seg_decay + ((size_t)(r * max_seg + seg + 1) * H + h) * D;
+#pragma unroll
+        for (int i = 0; i < LA_CPT; ++i)
+            if (c_lo + i < c_hi) {
+                if (col) Ld[(size_t)(c_lo + i) * V + j] = S[i];
+                if (blockIdx.x == 0 && lane == 0) Ad[c_lo + i] = P[i];
+            }
+        return;
+    }
+    if (col && (MODE == 0 || seg == nseg - 1)) {
 #pragma unroll
         for (int i = 0; i < LA_CPT; ++i)
             if (c_lo + i < c_hi) Sg[(size_t)(c_lo + i) * V + j] = S[i];
     }
 }
 
+// start states of the segments 1 .. nseg-1 of every request, in place of their local end states; grid (D*V / 256, H, requests)
+__global__ void linattn_combine_kernel(const float* __restrict__ state, const int* __restrict__ req_q_len,
+                                       const int* __restrict__ req_slot, int H, int D, int V, int seg_len, int max_seg,
+                                       float* __restrict__ seg_state, const float* __restrict__ seg_decay) {
+    pdl_begin();
+    const int r = blockIdx.z, h = blockIdx.y;
+    const int req_len = req_q_len[r], slot = req_slot[r];
+    if (req_len <= 0 || slot < 0) return;
+    const int nseg = (req_len + seg_len - 1) / seg_len;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (nseg <= 1 || e >= D * V) return;
+    const int d = e / V;
+    float cur = state[(((size_t)slot * H + h) * D) * V + e];
+    seg_state[((size_t)(r * max_seg) * H + h) * D * V + e] = cur;
+    for (int sgm = 1; sgm < nseg; ++sgm) {
+        const size_t at = (size_t)(r * max_seg + sgm) * H + h;
+        cur = fmaf(seg_decay[at * D + d], cur, seg_state[at * D * V + e]);
+        seg_state[at * D * V + e] = cur;
+    }
+}
+
 // q, k: [n, H, D]; v, out: [n, H, V]; decay: [n, H, D] per key channel, or null with head_decay [H];
 // state: [slots, H, D, V].  Requests by start, length and state slot; a length of 0 or a slot of -1 is passed by.
+// seg_len > 0: portions longer than that are cut into segments that run side by side (at most max_seg a request, which
+// must cover the longest portion); seg_state holds requests * max_seg * H * D * V floats, seg_decay requests * max_seg * H * D.
 WLLM_API int wllm_linattn_scan(const float* q, const float* k, const float* v, const float* decay, const float* head_decay,
                                float* state, float* out, const int* req_q_start, const int* req_q_len, const int* req_slot,
-                               int requests, int H, int D, int V, cudaStream_t stream) {
+                               int requests, int H, int D, int V, int seg_len, int max_seg, float* seg_state, float* seg_decay,
+                               cudaStream_t stream) {
     if (requests <= 0) return WLLM_OK;
     if (H <= 0 || H > 65535 || requests > 65535 || D <= 0 || D > 32 * LA_CPT || V <= 0) return WLLM_BAD_SIZE;
     if (!decay && !head_decay) return WLLM_BAD_SIZE;
+    const bool cut = seg_len > 0 && max_seg > 1;
+    if (cut && (!seg_state || !seg_decay || (long long)requests * max_seg > 65535)) return WLLM_BAD_SIZE;
     const int warps = (D + LA_CPT - 1) / LA_CPT;
     const int cpt = (D + warps - 1) / warps;
-    const dim3 grid((V + LA_COLS - 1) / LA_COLS, H, requests);
+    const int vtiles = (V + LA_COLS - 1) / LA_COLS;
     const size_t smem = ((size_t)2 * LA_TT * ((decay ? 3 : 2) * D + LA_COLS) + 2 * warps * 32) * sizeof(float);
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(linattn_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(linattn_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        cudaError_t e = cudaSuccess;
+#define RAISE(K) if (e == cudaSuccess) e = cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)
+        RAISE((linattn_scan_kernel<true, 0>)); RAISE((linattn_scan_kernel<true, 1>)); RAISE((linattn_scan_kernel<true, 2>));
+        RAISE((linattn_scan_kernel<false, 0>)); RAISE((linattn_scan_kernel<false, 1>)); RAISE((linattn_scan_kernel<false, 2>));
+#undef RAISE
         if (e != cudaSuccess) return 1000 + (int)e;
         raised = true;
     }
-    if (decay)
-        return wllm_launch(linattn_scan_kernel<true>, grid, warps * 32, smem, stream, q, k, v, decay, head_decay, state, out,
-                           req_q_start, req_q_len, req_slot, H, D, V, cpt);
-    return wllm_launch(linattn_scan_kernel<false>, grid, warps * 32, smem, stream, q, k, v, decay, head_decay, state, out,
-                       req_q_start, req_q_len, req_slot, H, D, V, cpt);
+#define SCAN(PC, MODE, GRID) wllm_launch(linattn_scan_kernel<PC, MODE>, GRID, warps * 32, smem, stream, q, k, v, decay, head_decay, \
+        state, out, req_q_start, req_q_len, req_slot, H, D, V, cpt, seg_len, max_seg, seg_state, seg_decay)
+    if (!cut) {
+        const dim3 grid(vtiles, H, requests);
+        return decay ? SCAN(true, 0, grid) : SCAN(false, 0, grid);
+    }
+    const dim3 grid(vtiles, H, requests * max_seg);
+    int st = decay ? SCAN(true, 1, grid) : SCAN(false, 1, grid);
+    if (st != WLLM_OK) return st;
+    st = wllm_launch(linattn_combine_kernel, dim3((D * V + 255) / 256, H, requests), 256, 0, stream, (const float*)state,
+                     req_q_len, req_slot, H, D, V, seg_len, max_seg, seg_state, (const float*)seg_decay);
+    if (st != WLLM_OK) return st;
+    return decay ? SCAN(true, 2, grid) : SCAN(false, 2, grid);
+#undef SCAN
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -325,21 +325,23 @@ def decode_split_plan(heads: int, max_ctx: int, tile: int) -> tuple:
 
 def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, nq: int, nkv: int,
                          hd: int, page_size: int, window: int, scale: float, split_keys: int, max_splits: int,
-                         scratch: torch.Tensor) -> None:
-    """bfloat16 attention of the requests that bring one token (csrc/attention_mma.cu, decode)."""
-    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, scratch)
+                         scratch: torch.Tensor, sinks: torch.Tensor | None = None) -> None:
+    """bfloat16 attention of the requests that bring one token (csrc/attention_mma.cu, decode).
+    `sinks`: float32 [nq], one more term e^sink of every row's softmax denominator."""
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, scratch, sinks)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and scratch.dtype == torch.float32
     R = req_q_len.shape[0]
     assert scratch.numel() >= attention_mma_scratch_floats(R, nq, hd, max_splits)
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
-    _check(lib.wllm_attention_mma_decode(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
-                                         ctypes.c_longlong(k_pages.shape[0]),
-                                         _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
-                                         _ptr(_int32(req_ctx_len, "req_ctx_len")),
-                                         _ptr(_int32(block_table, "block_table")), block_table.shape[1], R, nq, nkv,
-                                         page_size, window, c_float(scale), split_keys, max_splits, _ptr(scratch),
-                                         _ptr(_status_word(q.device)), _stream()),
+    _check(lib.wllm_attention_mma_decode_sinks(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                               ctypes.c_longlong(k_pages.shape[0]),
+                                               _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
+                                               _ptr(_int32(req_ctx_len, "req_ctx_len")),
+                                               _ptr(_int32(block_table, "block_table")), block_table.shape[1], R, nq, nkv,
+                                               page_size, window, c_float(scale), split_keys, max_splits, _ptr(scratch),
+                                               _ptr(_status_word(q.device)), _ptr(sinks), _stream()),
            f"attention_mma_decode(head_dim={hd}, heads={nq}/{nkv})")
     global launches
     launches += 1 if max_splits > 1 else 0    # the merge kernel
@@ -377,25 +379,27 @@ def prefill_share_plan(q_lens, ctx_lens, nq: int, nkv: int, hd: int, skip_single
 
 def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, max_q_len: int,
                           nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
-                          skip_single: bool, split_above: int = 0, halves: torch.Tensor | None = None) -> None:
+                          skip_single: bool, split_above: int = 0, halves: torch.Tensor | None = None,
+                          sinks: torch.Tensor | None = None) -> None:
     """bfloat16 attention of the requests that bring several tokens (csrc/attention_mma.cu, prefill).
     split_above > 0 (head sizes in steps of 64): a tile of 128 rows that walks more than that many tiles of 64
     keys is computed by two CTAs, half of the keys each; `halves` (float32) holds their partial results."""
-    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, halves)
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, halves, sinks)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     if split_above > 0:
         assert hd % 64 == 0 and halves is not None and halves.dtype == torch.float32 and halves.is_contiguous()
         assert halves.numel() >= attention_prefill_halves_floats(req_q_len.shape[0], max_q_len, nq, nkv, hd)
     assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
-    _check(lib.wllm_attention_mma_prefill(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
-                                          ctypes.c_longlong(k_pages.shape[0]),
-                                          _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
-                                          _ptr(_int32(req_ctx_len, "req_ctx_len")),
-                                          _ptr(_int32(block_table, "block_table")), block_table.shape[1],
-                                          req_q_len.shape[0], max_q_len, nq, nkv, page_size, window, c_float(scale),
-                                          1 if skip_single else 0, split_above, _ptr(halves) if split_above > 0 else None,
-                                          _ptr(_status_word(q.device)), _stream()),
+    _check(lib.wllm_attention_mma_prefill_sinks(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                                ctypes.c_longlong(k_pages.shape[0]),
+                                                _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
+                                                _ptr(_int32(req_ctx_len, "req_ctx_len")),
+                                                _ptr(_int32(block_table, "block_table")), block_table.shape[1],
+                                                req_q_len.shape[0], max_q_len, nq, nkv, page_size, window, c_float(scale),
+                                                1 if skip_single else 0, split_above, _ptr(halves) if split_above > 0 else None,
+                                                _ptr(_status_word(q.device)), _ptr(sinks), _stream()),
            f"attention_mma_prefill(head_dim={hd}, heads={nq}/{nkv})")
 
 
@@ -674,13 +678,43 @@ def linattn_prepare(fused, parts: int, q_off: int, k_off: int, v_off: int, heads
                                     c_float(tau), _ptr(q), _ptr(k), _ptr(v), _ptr(decay), _stream()), "linattn_prepare")
 
 
+LINATTN_SEGMENT_FROM = 128     # portions of at least this many tokens may be cut into segments that run side by side
+LINATTN_MIN_SEGMENT = 32
+
+
+def linattn_segment_plan(max_q_len: int, requests_multi: int, heads: int, vdim: int) -> tuple:
+    """(seg_len, max_seg) for the recurrence over a step whose longest portion has max_q_len tokens; (0, 1): every
+    request is walked in one go.  A walk is sequential in its tokens, and heads x tiles of 32 value columns x requests
+    walks seldom fill the device; a long portion is therefore cut into segments that run side by side and are walked
+    twice (csrc/linear_attention.cu), as many as the device holds at once (about eight CTAs an SM), of at least
+    LINATTN_MIN_SEGMENT tokens."""
+    if max_q_len < LINATTN_SEGMENT_FROM:
+        return 0, 1
+    walks = max(1, requests_multi) * heads * -(-vdim // 32)
+    wanted = (8 * sm_count()) // walks
+    if wanted < 3:            # two segments walked twice are no shorter than one walk
+        return 0, 1
+    seg_len = max(LINATTN_MIN_SEGMENT, -(-(-(-max_q_len // wanted)) // 8) * 8)
+    max_seg = -(-max_q_len // seg_len)
+    return (seg_len, max_seg) if max_seg > 2 else (0, 1)
+
+
 def linattn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay, head_decay, state: torch.Tensor,
                  out: torch.Tensor, req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_slot: torch.Tensor, heads: int,
-                 dim: int, vdim: int) -> torch.Tensor:
+                 dim: int, vdim: int, seg_len: int = 0, max_seg: int = 1, seg_state: torch.Tensor | None = None,
+                 seg_decay: torch.Tensor | None = None) -> torch.Tensor:
     """S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t over every request's tokens of the step, from and to the
     request's row of `state` [slots, heads, dim, vdim] (float32).  `decay` [n, heads*dim] per key channel, or None
-    with `head_decay` [heads]."""
-    _need_cuda(q, k, v, decay, head_decay, state, out, req_q_start, req_q_len, req_slot)
+    with `head_decay` [heads].  With seg_len > 0 and max_seg > 1 (linattn_segment_plan) portions are cut into segments
+    of seg_len tokens that run side by side; seg_state (requests * max_seg * heads * dim * vdim floats) and seg_decay
+    (requests * max_seg * heads * dim) are their scratch."""
+    _need_cuda(q, k, v, decay, head_decay, state, out, req_q_start, req_q_len, req_slot, seg_state, seg_decay)
+    R = req_q_len.shape[0]
+    if seg_len > 0 and max_seg > 1:
+        assert seg_state.dtype == seg_decay.dtype == torch.float32 and seg_state.is_contiguous() and seg_decay.is_contiguous()
+        assert seg_state.numel() >= R * max_seg * heads * dim * vdim and seg_decay.numel() >= R * max_seg * heads * dim
+        global launches
+        launches += 2         # the segments' first walk and the kernel that chains their states
     n = q.shape[0]
     assert all(t.dtype == torch.float32 and t.is_contiguous() for t in (q, k, v, state, out))
     assert q.shape == k.shape == (n, heads * dim) and v.shape == out.shape == (n, heads * vdim)
@@ -692,7 +726,8 @@ def linattn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay, head_
     lib = load_family("linear_attention")
     _check(lib.wllm_linattn_scan(_ptr(q), _ptr(k), _ptr(v), _ptr(decay), _ptr(head_decay), _ptr(state), _ptr(out),
                                  _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
-                                 _ptr(_int32(req_slot, "req_slot")), req_q_len.shape[0], heads, dim, vdim, _stream()),
+                                 _ptr(_int32(req_slot, "req_slot")), R, heads, dim, vdim, seg_len, max_seg,
+                                 _ptr(seg_state), _ptr(seg_decay), _stream()),
            f"linattn_scan(heads={heads}, dim={dim}, vdim={vdim})")
     return out
 

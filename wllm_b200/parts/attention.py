@@ -54,8 +54,8 @@ class PagedAttention:
         self.scale = float(self.hd) ** -0.5 if scale is None else float(scale)
         self.sink_name = spec.options.get("sink")
         self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
-        # the tensor-core kernels take equal head sizes and a plain softmax; everything else runs on the general ones
-        self.general = self.vd != self.hd or self.sink_name is not None
+        # the tensor-core kernels take keys and values of one size; other shapes run on the general kernels
+        self.general = self.vd != self.hd
         self.width = (self.nq + self.nkv) * self.hd + self.nkv * self.vd      # columns of the fused q|k|v row
         self.tag = ""                    # set by a mixer that runs this one beside another: keeps their buffers apart
         self.wqkv = self.wo = self.sinks = None
@@ -114,7 +114,7 @@ class PagedAttention:
             # Three kernels with one result, bit for bit, so the choice is one of speed alone.  Portions of prompts:
             # 32 rows of a request share every tile of keys.  Few rows over long contexts (decoding): a warp per
             # (row, chunk of 64 keys).  Otherwise a warp per row.
-            extra = {"vd": self.vd, "sinks": self.sinks} if self.general else {}
+            extra = {"vd": self.vd, "sinks": self.sinks} if (self.general or self.sinks is not None) else {}
             if ctx.num_multi > 0 and hd <= 256 and self.vd <= 256:
                 ops.paged_attention_simt_tiled(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len,
                                                table, ctx.max_q_len, nq, nkv, hd, ps, window, scale, **extra)
@@ -127,20 +127,21 @@ class PagedAttention:
                                      window, scale, scratch, chunks, **extra)
             return
         decode = ctx.num_single > 0 and nq // nkv <= 16
+        extra = {"sinks": self.sinks} if self.sinks is not None else {}
         if decode:
             R = ctx.n_requests
             # one CTA fits on an SM: every (request, kv head) is cut into parts so that the CTAs finish together
             # (planned for the context rounded up to 512 keys, so that a growing context seldom needs a new plan)
             split_keys, max_splits = ops.decode_split_plan(R * nkv, -(-ctx.max_ctx // 512) * 512, 32 if hd % 64 == 0 else 64)
-            scratch = ctx.buffer("attention_splits", (ops.attention_mma_scratch_floats(R, nq, hd, max_splits),),
+            scratch = ctx.buffer(self.tag + "attention_splits", (ops.attention_mma_scratch_floats(R, nq, hd, max_splits),),
                                  torch.float32)
             ops.attention_mma_decode(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
-                                     nq, nkv, hd, ps, window, scale, split_keys, max_splits, scratch)
+                                     nq, nkv, hd, ps, window, scale, split_keys, max_splits, scratch, **extra)
         if ctx.num_multi > 0 or not decode:
             split_above, halves = self._shared_tiles(ctx, skip_single=decode)
             ops.attention_mma_prefill(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
                                       ctx.max_q_len, nq, nkv, hd, ps, window, scale, skip_single=decode,
-                                      split_above=split_above, halves=halves)
+                                      split_above=split_above, halves=halves, **extra)
 
     def _shared_tiles(self, ctx, skip_single: bool):
         """Whether this step's prefill attention shares its heavy tiles between two CTAs (ops.prefill_share_plan),
@@ -160,4 +161,4 @@ class PagedAttention:
         if split_above <= 0:
             return 0, None
         floats = ops.attention_prefill_halves_floats(ctx.n_requests, ctx.max_q_len, nq, nkv, hd)
-        return split_above, ctx.buffer("attention_halves", (floats,), torch.float32)
+        return split_above, ctx.buffer(self.tag + "attention_halves", (floats,), torch.float32)

@@ -120,8 +120,15 @@ class LinearAttention:
                             low_off=col0 + self.off_low if low else -1, w2=self.w_up, b2=self.b_up,
                             tau=self.tau if low else 1.0, decay=decay)
         o = ctx.buffer(self.tag + "la_o", (n, H * V), f32)
+        # long portions are cut into segments that run side by side; the plan is a function of the step's shape alone
+        seg_len, max_seg = ops.linattn_segment_plan(ctx.max_q_len, ctx.num_multi, H, V)
+        seg_state = seg_decay = None
+        if max_seg > 1:
+            R = ctx.n_requests
+            seg_state = ctx.buffer(self.tag + "la_seg_state", (R * max_seg * H * D * V,), f32)
+            seg_decay = ctx.buffer(self.tag + "la_seg_decay", (R * max_seg * H * D,), f32)
         ops.linattn_scan(q, k, v, decay, self.head_decay, ctx.state(cache.state_names["state"]), o, ctx.req_q_start,
-                         ctx.req_q_len, ctx.req_slot, H, D, V)
+                         ctx.req_q_len, ctx.req_slot, H, D, V, seg_len, max_seg, seg_state, seg_decay)
         gated = ctx.buffer(self.tag + "la_gated", (n, H * V), self.model_dtype)
         ops.head_gate_norm(o, fused, parts, col0 + self.off_g, self.norm_weight, self.eps, gated, H, V)
         return as_branch(ops.project(gated, self.wo, lambda name, shape, dt: ctx.buffer(self.tag + "la_out_" + name, shape, dt)))
