@@ -15,6 +15,14 @@ are seeded uniform random, the caches of the device-timed runs are filled with r
 keys and values (synthetic context); the end-to-end run prefills its prompts for real.
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from
 the fallback figures of an earlier measurement on this pool.
+
+    python bench.py --design pesanex [--steps K] [--warmup W] [--batch 8] [--context 2048]
+
+is another workload (the default one and its line are unchanged): Pesanex models at layer sizes of real models
+(random weights) beside a Gemma of the same width, feed-forward, attention heads and number of layers: prefill of one
+2,048-token prompt and decode at `batch` requests, device-timed; and the new design's kernels one by one at those
+shapes (L2 flushed before each timed launch), each with the bytes it must move over the measured copy bandwidth,
+beside the like kernel of the Gemma layer.  One JSON line.
 """
 from __future__ import annotations
 
@@ -97,12 +105,14 @@ def fill_synthetic_context(runner, caches, context: int, seed: int) -> None:
         runner.cache.commit(rc, context)
     g = torch.Generator(device=runner.device).manual_seed(seed)
     for group in runner.cache.groups:
-        pages = group.pages
-        flat = pages.view(-1)
-        step = 1 << 26
-        for i in range(0, flat.numel(), step):
-            n = min(step, flat.numel() - i)
-            flat[i:i + n] = torch.randn(n, generator=g, device=runner.device, dtype=torch.float32).to(pages.dtype)
+        for pages in (group.pages, group.key_pages, group.value_pages):
+            if pages is None:
+                continue
+            flat = pages.view(-1)
+            step = 1 << 26
+            for i in range(0, flat.numel(), step):
+                n = min(step, flat.numel() - i)
+                flat[i:i + n] = torch.randn(n, generator=g, device=runner.device, dtype=torch.float32).to(pages.dtype)
 
 
 def decode_run(model, engine_cfg, batch: int, context: int, steps: int, warmup: int, page_size: int, regions: int = 1):
@@ -352,6 +362,190 @@ def reference_arm(args) -> int:
     return 0
 
 
+PESANEX_SIZES = {
+    # name: width, feed-forward, attention (heads, kv heads, head size), linear attention (heads, key size, value size, rank)
+    "2b": dict(width=2048, ff=16384, attn=(8, 1, 256), lin=(8, 128, 256, 64), vocab=32000, layers=4),
+    "7b": dict(width=4096, ff=14336, attn=(32, 8, 128), lin=(16, 128, 256, 64), vocab=32000, layers=4),
+}
+
+
+def pesanex_config(size: dict, layout: str) -> dict:
+    """'parallel': every layer runs attention with sinks beside gated linear attention, and a feed-forward (a Gemma layer
+    plus the second mixer); 'mixed': gated linear attention, the parallel layer, retention, the parallel layer."""
+    nq, nkv, hd = size["attn"]
+    lh, ld, lv, rank = size["lin"]
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": size["ff"]},
+           "mixer": {"left": {"heads": nq, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                              "rot": {"dims": hd // 2, "base": 1e6}},
+                     "right": {"heads": lh, "dim": ld, "vdim": lv, "tau": 16.0, "rank": rank}}}
+    gla = {"type": "gla", "mlp": None, "mixer": {"heads": lh, "dim": ld, "vdim": lv, "tau": 16.0, "rank": rank}}
+    ret = {"type": "retention", "mlp": None,
+           "mixer": {"heads": lh, "dim": ld, "vdim": lv, "rot": {"dims": ld, "base": 1e6},
+                     "decay": [1.0 - 2.0 ** (-5 - 6.0 * i / max(1, lh - 1)) for i in range(lh)]}}
+    layers = [par] * size["layers"] if layout == "parallel" else ([gla, par, ret, par] * size["layers"])[:size["layers"]]
+    return {"architecture": "Pesanex", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def timed_us(fn, flush, repeats: int = 10) -> float:
+    """Median device time of fn() in microseconds: three warm-up launches, then `repeats` timed ones, each behind a
+    write of a buffer larger than the L2."""
+    import torch
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(repeats):
+        flush.add_(1.0)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) * 1e3)
+    return statistics.median(times)
+
+
+def pesanex_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int) -> dict:
+    """The new design's kernels alone at one size's shapes, and the like kernels of the Gemma layer: microseconds, the bytes
+    each must move at the measured copy bandwidth (`floor_us`), and how many times the floor it takes (`x_floor`)."""
+    import torch
+    from wllm_b200.kernels import ops
+    dev, bf, f32 = "cuda:0", torch.bfloat16, torch.float32
+    flush = torch.zeros(160 << 20, dtype=f32, device=dev)
+    W = size["width"]
+    nq, nkv, hd = size["attn"]
+    H, D, V, rank = size["lin"]
+    ps = 64
+    out = {}
+
+    def row(name, fn, bytes_moved, flops=0.0):
+        us = timed_us(fn, flush)
+        floor = max(bytes_moved / (pk["hbm_gbs"] * 1e3), flops / (pk["bf16_tflops"] * 1e6))
+        out[name] = {"us": round(us, 1), "floor_us": round(floor, 2), "x_floor": round(us / max(floor, 1e-9), 1)}
+
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def rnd(*shape, dtype=f32):
+        return torch.randn(*shape, generator=g, device=dev, dtype=f32).to(dtype)
+    # ---- norms: Gemma's residual norm; the centred norm; the norm of a branch; the mean of two normed branches
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        resid, delta, w = rnd(n, W), rnd(n, W, dtype=bf), rnd(W, dtype=bf)
+        o = torch.empty(n, W, dtype=bf, device=dev)
+        o32 = torch.empty(n, W, device=dev)
+        row(f"{tag}/gemma rmsnorm+add", lambda: ops.rmsnorm(resid, delta, w, 1e-6, 1.0, o), n * W * (4 + 4 + 2 + 2))
+        row(f"{tag}/layernorm+add", lambda: ops.rmsnorm(resid, o32, w, 1e-6, 0.0, o, center=True), n * W * (4 + 4 + 4 + 2))
+        row(f"{tag}/branch layernorm", lambda: ops.branch_norm((delta, 0), w, o32, 1e-6, center=True), n * W * (2 + 4))
+        row(f"{tag}/mean of two normed branches", lambda: ops.branch_norm((delta, 0), w, o32, 1e-6, factor=0.5, b=(delta, 0), weight_b=w),
+            n * W * (2 + 2 + 4))
+    # ---- rotary + cache write, with and without unit-norm heads
+    pages = batch * (-(-(context + 1) // ps)) + -(-T // ps) + 1
+    kp, vp = rnd(pages, nkv, ps, hd, dtype=bf), rnd(pages, nkv, ps, hd, dtype=bf)
+    inv_freq = torch.arange(hd // 4, device=dev, dtype=f32).neg().div(hd // 4).exp()
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        qkv = rnd(n, (nq + 2 * nkv) * hd, dtype=bf)
+        qo = torch.empty(n, nq * hd, dtype=bf, device=dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        slots = torch.arange(n, dtype=torch.int32, device=dev)
+        moved = n * (nq + 2 * nkv) * hd * 2 * 2
+        row(f"{tag}/gemma rotary+cache write", lambda: ops.rope_kv_write(qkv, qo, pos, slots, inv_freq, kp, vp, nq, nkv, hd, hd // 2, ps), moved)
+        row(f"{tag}/rotary+unit norm+cache write",
+            lambda: ops.rope_kv_write(qkv, qo, pos, slots, inv_freq, kp, vp, nq, nkv, hd, hd // 2, ps, unit_norm_eps=1e-6), moved)
+    # ---- attention: prefill of T tokens, decode of `batch` requests over `context` keys; with and without sinks
+    sinks = rnd(nq)
+    one = torch.ones(1, dtype=torch.int32, device=dev)
+    table = torch.arange(-(-T // ps), dtype=torch.int32, device=dev).view(1, -1)
+    q = rnd(T, nq * hd, dtype=bf)
+    ao = torch.empty(T, nq * hd, dtype=bf, device=dev)
+    flops = 4.0 * nq * hd * T * T / 2
+    for name, extra in (("gemma attention", {}), ("attention with sinks", {"sinks": sinks})):
+        row(f"prefill/{name}", lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, 0,
+                                                                  hd ** -0.5, skip_single=False, **extra), T * nq * hd * 4, flops)
+    per = -(-(context + 1) // ps)
+    dtable = torch.arange(batch * per, dtype=torch.int32, device=dev).view(batch, per)
+    qd, od = rnd(batch, nq * hd, dtype=bf), torch.empty(batch, nq * hd, dtype=bf, device=dev)
+    starts, lens = torch.arange(batch, dtype=torch.int32, device=dev), torch.ones(batch, dtype=torch.int32, device=dev)
+    ctxs = lens * context
+    split_keys, max_splits = ops.decode_split_plan(batch * nkv, -(-context // 512) * 512, 32 if hd % 64 == 0 else 64)
+    scratch = torch.empty(ops.attention_mma_scratch_floats(batch, nq, hd, max_splits), device=dev)
+    for name, extra in (("gemma attention", {}), ("attention with sinks", {"sinks": sinks})):
+        row(f"decode/{name}", lambda: ops.attention_mma_decode(qd, od, kp, vp, starts, lens, ctxs, dtable, nq, nkv, hd, ps, 0, hd ** -0.5,
+                                                                 split_keys, max_splits, scratch, **extra), batch * context * nkv * hd * 2 * 2)
+    # ---- the recurrence: its inputs from the fused product, the walk, the heads' norm and gate
+    w2, b2, nw = rnd(H * D, rank, dtype=bf), rnd(H * D, dtype=bf), rnd(V, dtype=bf)
+    state = torch.zeros(batch + 1, H, D, V, device=dev)
+    for n, tag, R in ((T, "prefill", 1), (batch, "decode", batch)):
+        fused = rnd(n, 2 * H * D + 2 * H * V + rank, dtype=bf)
+        bufs = [torch.empty(n, H * D, device=dev), torch.empty(n, H * D, device=dev), torch.empty(n, H * V, device=dev)]
+        decay = torch.empty(n, H * D, device=dev)
+        pos = torch.arange(n, dtype=torch.int32, device=dev)
+        row(f"{tag}/recurrence inputs (decay from the low-rank map)",
+            lambda: ops.linattn_prepare(fused, 0, 0, H * D, 2 * H * D, H, D, V, pos, *bufs, q_scale=D ** -0.5,
+                                        low_off=2 * H * D + 2 * H * V, w2=w2, b2=b2, tau=16.0, decay=decay),
+            n * ((2 * H * D + H * V + rank) * 2 + (3 * H * D + H * V) * 4))
+        o = torch.empty(n, H * V, device=dev)
+        if R == 1:
+            rs, rl, rslot = one * 0, one * n, one * 0
+            seg_len, max_seg = ops.linattn_segment_plan(n, 1, H, V)
+        else:
+            rs, rl, rslot = starts, lens, starts
+            seg_len, max_seg = 0, 1
+        seg_state = torch.empty(R * max_seg * H * D * V, device=dev)
+        seg_decay = torch.empty(R * max_seg * H * D, device=dev)
+        walk_bytes = n * (3 * H * D + 2 * H * V) * 4 + R * 2 * H * D * V * 4
+        row(f"{tag}/recurrence" + (f" ({max_seg} segments of {seg_len})" if max_seg > 1 else ""),
+            lambda: ops.linattn_scan(bufs[0], bufs[1], bufs[2], decay, None, state, o, rs, rl, rslot, H, D, V, seg_len, max_seg,
+                                     seg_state, seg_decay), walk_bytes, 4.0 * n * H * D * V)
+        gated = torch.empty(n, H * V, dtype=bf, device=dev)
+        row(f"{tag}/head norm and gate", lambda: ops.head_gate_norm(o, fused, 0, 2 * H * D + H * V, nw, 1e-6, gated, H, V),
+            n * H * V * (4 + 2 + 2))
+    return out
+
+
+def pesanex_bench(args) -> int:
+    import torch
+    from wllm_b200.config import EngineConfig, GemmaConfig, PesanexConfig
+    from wllm_b200.engine import build_model
+    pk = peaks()
+    ps, T = args.page_size, 2048
+    context = args.context or 2048
+    engine_cfg = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=max(64, args.batch), cuda_graphs=not args.no_graphs)
+    sizes = {}
+    for name in args.sizes.split(","):
+        size = PESANEX_SIZES[name]
+        nq, nkv, hd = size["attn"]
+        models = {
+            "gemma": GemmaConfig.from_dict(dict(architectures=["GemmaForCausalLM"], vocab_size=size["vocab"], hidden_size=size["width"],
+                                                intermediate_size=size["ff"], num_hidden_layers=size["layers"],
+                                                num_attention_heads=nq, num_key_value_heads=nkv, head_dim=hd,
+                                                max_position_embeddings=8192)),
+            "pesanex_parallel": PesanexConfig.from_dict(pesanex_config(size, "parallel")),
+            "pesanex_mixed": PesanexConfig.from_dict(pesanex_config(size, "mixed")),
+        }
+        res = {}
+        for label, cfg in models.items():
+            model = build_model(None, engine_cfg.dtype, engine_cfg.device, config=cfg, random_seed=1)
+            pre_ms = prefill_run(model, engine_cfg, T, ps)
+            ms, launches, _, clocks, _ = decode_run(model, engine_cfg, args.batch, context, min(args.steps, 32), args.warmup, ps, 3)
+            res[label] = {"weights_gb": round(model.weight_bytes() / 1e9, 3), "prefill_tok_s": round(T / (pre_ms / 1e3), 1),
+                          "prefill_ms": round(pre_ms, 3), "decode_tok_s": round(args.batch / (ms / 1e3), 1),
+                          "decode_ms_per_step": round(ms, 4), "decode_launches": launches,
+                          "decode_weights_hbm_frac": round(model.weight_bytes() / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3),
+                          "clocks": clocks}
+            del model
+            torch.cuda.empty_cache()
+        sizes[name] = {"shape": size, "models": res}
+        if not args.no_points:
+            sizes[name]["kernels"] = pesanex_kernel_table(size, pk, T, args.batch, context)
+    print(json.dumps({"metric": "Pesanex beside Gemma at equal layer sizes: prefill tok/s @ 2048 tokens, decode tok/s",
+                      "design": "pesanex", "unit": "tokens/s", "n_gpus": 1, "steps": min(args.steps, 32), "warmup": args.warmup,
+                      "dtype": "bf16", "data": "synthetic (random weights, random token ids, random cached keys/values, zero states)",
+                      "config": {"global_batch": args.batch, "seq_len": context, "prefill_tokens": T, "page_size": ps,
+                                 "cuda_graphs": not args.no_graphs, "peaks": pk["source"],
+                                 "l2": "kernel table: a 640 MB buffer is written before every timed launch"},
+                      "peaks": pk, "sizes": sizes}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -366,6 +560,9 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--design", default="gemma", choices=["gemma", "pesanex"],
+                    help="gemma: the default workload; pesanex: Pesanex models beside a Gemma of equal layer sizes (another line)")
+    ap.add_argument("--sizes", default="2b,7b", help="--design pesanex: which of the layer sizes to run (2b, 7b)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -373,6 +570,8 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design == "pesanex":
+        return pesanex_bench(args)
     import torch
     from wllm_b200.config import EngineConfig, GemmaConfig
     from wllm_b200.engine import build_model

@@ -277,11 +277,11 @@ def test_paged_attention_simt_tiled_is_the_walk_bit_for_bit(dtype, window, case)
 
 def test_paged_attention_refuses_unsupported_head_size():
     from wllm_b200.kernels import KernelError
-    q = torch.zeros(1, 40, device=DEV)
-    kp = torch.zeros(1, 1, 16, 40, device=DEV)
+    q = torch.zeros(1, 36, device=DEV)          # heads come in steps of 8 elements (16-byte loads of bfloat16)
+    kp = torch.zeros(1, 1, 16, 36, device=DEV)
     z = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(KernelError, match="size not supported"):
-        ops().paged_attention_simt(q, torch.empty_like(q), kp, kp, z, z, z.view(1, 1), 1, 1, 40, 16, 0, 1.0)
+        ops().paged_attention_simt(q, torch.empty_like(q), kp, kp, z, z, z.view(1, 1), 1, 1, 36, 16, 0, 1.0)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -98,6 +98,24 @@ def test_long_decoding_keeps_the_state(setups, dtype):
     close_enough(traces.run_in_process(runner, steps), ref, dtype)
 
 
+def test_decoding_from_captured_graphs_advances_the_state_once_a_step(setups):
+    """The run that warms a capture up must leave no trace in the state slots; rows under graphs are the eager rows."""
+    folder, reqs, ref = setups["plain"]
+    some = {k: reqs[k] for k in ("r1", "r2", "r5")}
+    steps = traces.tail_singly(some, 24)
+    rows = {}
+    for graphs in (False, True):
+        runner = runner_for(folder, torch.float32, 16, -(-traces.peak_tokens(steps) // 16), poison=False)
+        assert runner.model.graph_safe
+        if graphs:
+            runner.enable_graphs()
+        rows[graphs] = traces.run_in_process(runner, steps)
+        assert (runner.graph_launches > 0) == graphs
+        close_enough(rows[graphs], {k: v for k, v in ref.items() if k[0] in some}, torch.float32)
+    bad = sorted(k for k in rows[False] if not torch.equal(rows[False][k], rows[True][k]))
+    assert not bad, f"first differing (request, position) {bad[0]}"
+
+
 @pytest.mark.parametrize("name", ["mix", "plain"])
 def test_long_portions_cut_into_segments(setups, name, monkeypatch):
     """The recurrence over a long portion runs as segments side by side (local end states, chained, walked again);

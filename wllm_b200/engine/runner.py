@@ -265,8 +265,9 @@ class ModelRunner:
     # -- captured decode steps -------------------------------------------------------------
     def enable_graphs(self) -> None:
         """Replay a captured CUDA graph for steps in which every request brings one token and
-        wants its logits (a decode step), if every part of the model is `graph_safe` and none keeps
-        per-request state; other models step eagerly.  One graph per (number of requests, table width);
+        wants its logits (a decode step), if every part of the model is `graph_safe`; other models step
+        eagerly.  Parts that keep per-request state read and write it through the step's device arrays (state slot
+        per request), so a replay advances the state of the requests it is given.  One graph per (number of requests, table width);
         the index arrays live at fixed device addresses and are rewritten before each replay.
         The reference captures its decode step in batch-size buckets the same way
         (src/wllm/engine/cuda_graph_decoder.py:34-178)."""
@@ -296,8 +297,13 @@ class ModelRunner:
             arena, saved, saved_views = {}, self._arena, self._views
             self._arena, self._views = arena, {}     # the capture's buffers are its own: eager steps do not write them
             try:
+                # per-request state advances with every run of a step: what the warm-up run did to it is undone, so
+                # that the replay below is this step's one and only run (pages are written twice with the same values)
+                states = {name: t.clone() for name, t in self.cache.slots.tensors.items()}
                 self.model.forward(ctx)                  # loads kernels and library handles outside the capture
                 torch.cuda.synchronize()
+                for name, t in states.items():
+                    self.cache.slots.tensors[name].copy_(t)
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launches
                 with torch.cuda.graph(graph):

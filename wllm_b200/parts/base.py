@@ -31,9 +31,10 @@ Interfaces (duck-typed; see the built-in parts for examples):
 
 A part may declare `graph_safe = True`: everything it launches depends on device data and on the step's
 size bounds alone (tokens, requests, table width, longest context rounded to the table's reach), never on
-host copies of the batch's contents, and running the same step twice leaves the same cache and state.  Decode
-steps are replayed from captured CUDA graphs only for models whose parts all say so and that declare no
-per-request state; any other model runs every step eagerly, whatever `cuda_graphs` asks for.
+host copies of the batch's contents; its state slots it finds through the step's device arrays, and a request
+that brings no token (length 0, a padded row of a captured step) leaves no trace.  Decode steps are replayed from
+captured CUDA graphs only for models whose parts all say so; any other model runs every step eagerly, whatever
+`cuda_graphs` asks for.
 """
 from __future__ import annotations
 
