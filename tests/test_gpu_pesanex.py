@@ -181,6 +181,31 @@ def test_centred_norm_and_norm_of_a_branch(H):
     assert (y.cpu().double() - want).abs().max() < 1e-5
 
 
+@pytest.mark.parametrize("H", [96, 1000, 4099])
+@pytest.mark.parametrize("two", [False, True])
+def test_the_norm_behind_a_sublayer_inside_the_next_norm(H, two):
+    """One kernel: the branch (or the mean of two normed branches) through its own layer norm, added to the residual,
+    and the residual's next norm; also at selected rows, where the residual stays as it is."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(H + two)
+    n = 6
+    x, a, b = torch.randn(n, H, generator=g) * 2, torch.randn(2, n, H, generator=g), (torch.randn(n, H, generator=g) * 3).bfloat16()
+    wa, wb, wp, w = (torch.randn(H, generator=g) for _ in range(4))
+    u = a.sum(0).double()
+    if two:
+        u = 0.5 * (plain.unit_rms(u, 1e-6) * wa.double() + plain.unit_rms(b.double(), 1e-6) * wb.double())
+    r = x.double() + plain.layer_norm(u, wp.double(), 1e-5)
+    want = plain.layer_norm(r, w.double(), 1e-5)
+    more = dict(gain_a=wa.to(DEV), b=(b.to(DEV), 0), gain_b=wb.to(DEV), inner_eps=1e-6, factor=0.5) if two else {}
+    resid, out = x.to(DEV), torch.empty(n, H, device=DEV)
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    some = ops.sandwich_norm(resid, (a.to(DEV), 2), torch.empty(2, H, device=DEV), wp.to(DEV), True, 1e-5, w.to(DEV), 0.0, True,
+                             1e-5, rows=rows, **more)
+    assert torch.equal(resid.cpu(), x) and (some.cpu().double() - want[[4, 1]]).abs().max() < 2e-5
+    ops.sandwich_norm(resid, (a.to(DEV), 2), out, wp.to(DEV), True, 1e-5, w.to(DEV), 0.0, True, 1e-5, **more)
+    assert (out.cpu().double() - want).abs().max() < 2e-5 and (resid.cpu().double() - r).abs().max() < 1e-5
+
+
 def paged(dense, page_size, perm):
     """dense [T, heads, d] -> pool [pages, heads, page_size, d] with token t in page perm[t // page_size]."""
     T, heads, d = dense.shape

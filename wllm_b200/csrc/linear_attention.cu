@@ -13,8 +13,8 @@
 //                           split-K slabs): q and k turned by the rotary angle of the token's position (optional),
 //                           scaled, v copied, and the decay of every key channel worked out from a low-rank map:
 //                               z = W2 (x W1^T) + b,   a = sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau)
-//   wllm_linattn_scan       the recurrence.  Grid (tiles of 32 value columns, heads, requests); a lane owns one
-//                           column of S, a warp a run of at most 16 key channels of it, in registers.  Tokens
+//   wllm_linattn_scan       the recurrence.  Grid (tiles of 64 value columns, heads, requests); a lane owns two
+//                           columns of S, a warp a run of at most 16 key channels of them, in registers.  Tokens
 //                           arrive in tiles of 8 through a two-stage cp.async ring; the warps' partial dot products of a
 //                           token meet in shared memory and are added in warp order.  Long portions of prompts are cut
 //                           into segments that are walked side by side: from zero for their local end states, which a
@@ -34,50 +34,84 @@ __device__ __forceinline__ float la_in(const void* p, int dtype, int parts, size
 }
 
 // ---------------------------------------------------------------------------------------------------
-// prepare: grid (tokens, heads)
+// prepare: grid (tiles of PREP_TT tokens, heads), 128 threads
 // ---------------------------------------------------------------------------------------------------
-__global__ void linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_stride, int parts, size_t part_stride,
-                                       int q_off, int k_off, int v_off, int a_off, int H, int D, int V, int rank,
-                                       const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim,
-                                       float q_scale, float k_scale, const void* __restrict__ w2, const void* __restrict__ b2,
-                                       int w_dtype, float inv_tau, float* __restrict__ q, float* __restrict__ k,
-                                       float* __restrict__ v, float* __restrict__ decay) {
-    extern __shared__ float low[];               // the low-rank vector of the token
-    pdl_launch_dependents();
-    const int t = blockIdx.x, h = blockIdx.y;
-    const float pos = (float)positions[t];
+constexpr int PREP_TT = 8;       // tokens of a CTA: the head's slab of the low-rank matrix is read once for all of them
+constexpr int PREP_RK = 32;      // columns of the low-rank map taken at a time
+
+__global__ void __launch_bounds__(128)
+linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_stride, int parts, size_t part_stride,
+                       int q_off, int k_off, int v_off, int a_off, int n, int H, int D, int V, int rank,
+                       const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim,
+                       float q_scale, float k_scale, const void* __restrict__ w2, const void* __restrict__ b2,
+                       int w_dtype, float inv_tau, float* __restrict__ q, float* __restrict__ k,
+                       float* __restrict__ v, float* __restrict__ decay) {
+    __shared__ float w_s[128][PREP_RK + 1];      // [channel of the chunk][column], padded against bank conflicts
+    __shared__ float low_s[PREP_TT][PREP_RK];
+    pdl_begin();
+    const int t_lo = blockIdx.x * PREP_TT, h = blockIdx.y;
+    const int count = min(PREP_TT, n - t_lo);
     const int half = rot_dim >> 1;
-    pdl_wait();
-    const size_t row = (size_t)t * row_stride;
-    if (a_off >= 0) {
-        for (int r = threadIdx.x; r < rank; r += blockDim.x) low[r] = la_in(fused, in_dtype, parts, part_stride, row + a_off + r);
-        __syncthreads();
-    }
-    for (int which = 0; which < 2; ++which) {
-        const int off = (which ? k_off : q_off) + h * D;
-        float* dst = (which ? k : q) + ((size_t)t * H + h) * D;
-        const float scale = which ? k_scale : q_scale;
-        for (int j = threadIdx.x; j < half; j += blockDim.x) {
-            float sn, cs, y1, y2;
-            sincosf(pos * inv_freq[j], &sn, &cs);
-            rotate_pair(la_in(fused, in_dtype, parts, part_stride, row + off + j),
-                        la_in(fused, in_dtype, parts, part_stride, row + off + j + half), sn, cs, y1, y2);
-            dst[j] = y1 * scale;
-            dst[j + half] = y2 * scale;
+    for (int tt = 0; tt < count; ++tt) {
+        const int t = t_lo + tt;
+        const size_t row = (size_t)t * row_stride;
+        const float pos = (float)positions[t];
+        for (int which = 0; which < 2; ++which) {
+            const int off = (which ? k_off : q_off) + h * D;
+            float* dst = (which ? k : q) + ((size_t)t * H + h) * D;
+            const float scale = which ? k_scale : q_scale;
+            for (int j = threadIdx.x; j < half; j += blockDim.x) {
+                float sn, cs, y1, y2;
+                sincosf(pos * inv_freq[j], &sn, &cs);
+                rotate_pair(la_in(fused, in_dtype, parts, part_stride, row + off + j),
+                            la_in(fused, in_dtype, parts, part_stride, row + off + j + half), sn, cs, y1, y2);
+                dst[j] = y1 * scale;
+                dst[j + half] = y2 * scale;
+            }
+            for (int c = rot_dim + threadIdx.x; c < D; c += blockDim.x)
+                dst[c] = la_in(fused, in_dtype, parts, part_stride, row + off + c) * scale;
         }
-        for (int c = rot_dim + threadIdx.x; c < D; c += blockDim.x)
-            dst[c] = la_in(fused, in_dtype, parts, part_stride, row + off + c) * scale;
+        for (int c = threadIdx.x; c < V; c += blockDim.x)
+            v[((size_t)t * H + h) * V + c] = la_in(fused, in_dtype, parts, part_stride, row + v_off + h * V + c);
     }
-    for (int c = threadIdx.x; c < V; c += blockDim.x)
-        v[((size_t)t * H + h) * V + c] = la_in(fused, in_dtype, parts, part_stride, row + v_off + h * V + c);
-    if (a_off >= 0) {
-        for (int c = threadIdx.x; c < D; c += blockDim.x) {
-            const size_t ch = (size_t)h * D + c;
-            float z = la_any(b2, w_dtype, ch);
-            for (int r = 0; r < rank; ++r) z = fmaf(low[r], la_any(w2, w_dtype, ch * rank + r), z);
-            // log(sigmoid(z)) = min(z, 0) - log(1 + e^-|z|), exact at both ends
-            const float log_sig = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
-            decay[((size_t)t * H + h) * D + c] = expf(log_sig * inv_tau);
+    if (a_off < 0) return;
+    // z[token][channel] = b2[channel] + sum_r low[token][r] * w2[channel][r]: a thread a channel, PREP_TT sums each;
+    // the sum over r runs in ascending order whatever the tiling
+    for (int c0 = 0; c0 < D; c0 += 128) {
+        const int c = c0 + threadIdx.x;
+        const size_t ch = (size_t)h * D + min(c, D - 1);
+        float z[PREP_TT];
+        const float bias = la_any(b2, w_dtype, ch);
+#pragma unroll
+        for (int tt = 0; tt < PREP_TT; ++tt) z[tt] = bias;
+        for (int r0 = 0; r0 < rank; r0 += PREP_RK) {
+            const int rk = min(PREP_RK, rank - r0);
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < 128 * PREP_RK; idx += blockDim.x) {
+                const int cc = idx / PREP_RK, r = idx % PREP_RK;
+                w_s[cc][r] = (c0 + cc < D && r < rk) ? la_any(w2, w_dtype, ((size_t)h * D + c0 + cc) * rank + r0 + r) : 0.f;
+            }
+            for (int idx = threadIdx.x; idx < PREP_TT * PREP_RK; idx += blockDim.x) {
+                const int tt = idx / PREP_RK, r = idx % PREP_RK;
+                low_s[tt][r] = (tt < count && r < rk)
+                    ? la_in(fused, in_dtype, parts, part_stride, (size_t)(t_lo + tt) * row_stride + a_off + r0 + r) : 0.f;
+            }
+            __syncthreads();
+#pragma unroll 8
+            for (int r = 0; r < PREP_RK; ++r) {
+                const float w = w_s[threadIdx.x][r];
+#pragma unroll
+                for (int tt = 0; tt < PREP_TT; ++tt) z[tt] = fmaf(low_s[tt][r], w, z[tt]);
+            }
+        }
+        if (c < D) {
+#pragma unroll
+            for (int tt = 0; tt < PREP_TT; ++tt) {
+                if (tt >= count) break;
+                // log(sigmoid(z)) = min(z, 0) - log(1 + e^-|z|), exact at both ends
+                const float log_sig = fminf(z[tt], 0.f) - log1pf(expf(-fabsf(z[tt])));
+                decay[((size_t)(t_lo + tt) * H + h) * D + c] = expf(log_sig * inv_tau);
+            }
         }
     }
 }
@@ -89,21 +123,20 @@ WLLM_API int wllm_linattn_prepare(const void* fused, int in_dtype, int row_strid
                                   cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (H <= 0 || H > 65535 || D <= 0 || V <= 0 || parts < 1 || rot_dim < 0 || rot_dim > D || (rot_dim & 1)) return WLLM_BAD_SIZE;
-    if (a_off >= 0 && (rank <= 0 || rank > 8192 || !(tau > 0.f) || !w2 || !b2 || !decay)) return WLLM_BAD_SIZE;
+    if (a_off >= 0 && (rank <= 0 || !(tau > 0.f) || !w2 || !b2 || !decay)) return WLLM_BAD_SIZE;
     if ((in_dtype != WLLM_BF16 && in_dtype != WLLM_F32) || (a_off >= 0 && w_dtype != WLLM_BF16 && w_dtype != WLLM_F32))
         return WLLM_BAD_DTYPE;
-    const int threads = D >= 128 ? 128 : 64;
-    return wllm_launch(linattn_prepare_kernel, dim3(n, H), threads, a_off >= 0 ? (size_t)rank * sizeof(float) : 0, stream, fused,
-                       in_dtype, row_stride, parts, (size_t)part_stride, q_off, k_off, v_off, a_off, H, D, V, rank, positions,
+    return wllm_launch(linattn_prepare_kernel, dim3((n + PREP_TT - 1) / PREP_TT, H), 128, 0, stream, fused,
+                       in_dtype, row_stride, parts, (size_t)part_stride, q_off, k_off, v_off, a_off, n, H, D, V, rank, positions,
                        inv_freq, rot_dim, q_scale, k_scale, w2, b2, w_dtype, a_off >= 0 ? 1.0f / tau : 0.f, q, k, v, decay);
 }
 
 // ---------------------------------------------------------------------------------------------------
 // scan
 // ---------------------------------------------------------------------------------------------------
-constexpr int LA_CPT = 16;       // key channels a thread holds of its column of S
+constexpr int LA_CPT = 16;       // key channels a thread holds of each of its columns of S (a multiple of 4)
 constexpr int LA_TT = 8;         // tokens of a tile
-constexpr int LA_COLS = 32;      // value columns of a CTA (one a lane)
+constexpr int LA_COLS = 64;      // value columns of a CTA: two a lane (lane and lane + 32)
 
 __device__ __forceinline__ void la_cp4(float* smem_dst, const float* src) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -118,14 +151,19 @@ __device__ __forceinline__ void la_cp4(float* smem_dst, const float* src) {
 //         start_(j+1) = diag(A_j) start_j + L_j, start_0 = the slot's state (copied beside them).
 // MODE 2  every segment again, from its start state, with outputs; the last one leaves the request's new state.
 // The state that a token meets is the same up to rounding in all modes; the arithmetic from there is the same.
+//
+// A warp holds a run of `cpt` key channels (a multiple of 4, at most 16) of 64 columns of S: a lane two columns, in
+// registers.  A token's q, k and decay are the same for all lanes: they are read from shared memory four channels at
+// a time, and with two columns a lane every such read feeds eight multiply-adds; one column a lane and one channel
+// a read left the kernel waiting for shared memory (a read a multiply-add).
 template <bool PER_CHANNEL, int MODE>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(512)
 linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                     const float* __restrict__ decay, const float* __restrict__ head_decay, float* __restrict__ state,
                     float* __restrict__ out, const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
                     const int* __restrict__ req_slot, int H, int D, int V, int cpt, int seg_len, int max_seg,
                     float* __restrict__ seg_state, float* __restrict__ seg_decay) {
-    extern __shared__ float la_smem[];
+    extern __shared__ __align__(16) float la_smem[];
     pdl_begin();
     const int r = MODE == 0 ? blockIdx.z : blockIdx.z / max_seg, seg = MODE == 0 ? 0 : blockIdx.z % max_seg, h = blockIdx.y;
     const int req_len = req_q_len[r], slot = req_slot[r];
@@ -136,22 +174,26 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
     const int q_len = MODE == 0 ? req_len : min(req_len - tok_lo, seg_len);      // tokens of this walk
     const int t0 = req_q_start[r] + tok_lo;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    const int j = blockIdx.x * LA_COLS + lane;                // this lane's column of S
-    const bool col = j < V;
+    const int j0 = blockIdx.x * LA_COLS + lane, j1 = j0 + 32;  // this lane's columns of S
+    const bool col0 = j0 < V, col1 = j1 < V;
     const int c_lo = warp * cpt, c_hi = min(D, c_lo + cpt);   // this warp's key channels
-    // shared memory: two stages of [q | k | (a) | v] for LA_TT tokens, then two rounds of the warps' partial sums
-    const int per_token = (PER_CHANNEL ? 3 : 2) * D + LA_COLS;
+    // shared memory: two stages of [q | k | (a) | v] for LA_TT tokens (each run of D padded to a multiple of 4), then
+    // two rounds of the warps' partial sums
+    const int Dp = (D + 3) & ~3, NA = PER_CHANNEL ? 3 : 2;
+    const int per_token = NA * Dp + LA_COLS;
     float* stage0 = la_smem;
-    float* red = la_smem + 2 * LA_TT * per_token;             // [2][warps][32]
+    float* red = la_smem + 2 * LA_TT * per_token;             // [2][warps][64]
 
-    float S[LA_CPT], P[LA_CPT];
+    float S0[LA_CPT], S1[LA_CPT], P[LA_CPT];
     float* Sg = state + (((size_t)slot * H + h) * D) * V;
     // (a request of several segments reads every start from the scratch, the first one too: its last segment
     // may write the slot before its first one has started)
-    const float* S0 = (MODE == 2 && nseg > 1) ? seg_state + (((size_t)(r * max_seg + seg) * H + h) * D) * V : Sg;
+    const float* St = (MODE == 2 && nseg > 1) ? seg_state + (((size_t)(r * max_seg + seg) * H + h) * D) * V : Sg;
 #pragma unroll
     for (int i = 0; i < LA_CPT; ++i) {
-        S[i] = (MODE != 1 && col && c_lo + i < c_hi) ? S0[(size_t)(c_lo + i) * V + j] : 0.f;
+        const bool ch = MODE != 1 && c_lo + i < c_hi;
+        S0[i] = (ch && col0) ? St[(size_t)(c_lo + i) * V + j0] : 0.f;
+        S1[i] = (ch && col1) ? St[(size_t)(c_lo + i) * V + j1] : 0.f;
         P[i] = 1.f;
     }
     const float fixed = PER_CHANNEL ? 0.f : head_decay[h];
@@ -159,18 +201,18 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
     auto load_tile = [&](int tile, int stage) {
         float* dst = stage0 + (size_t)stage * LA_TT * per_token;
         const int first = t0 + tile * LA_TT, count = min(LA_TT, q_len - tile * LA_TT);
-        for (int idx = threadIdx.x; idx < count * per_token; idx += blockDim.x) {
-            const int tt = idx / per_token, e = idx % per_token;
-            const size_t tok = (size_t)(first + tt);
-            const float* src;
-            if (e < D) src = q + (tok * H + h) * D + e;
-            else if (e < 2 * D) src = k + (tok * H + h) * D + (e - D);
-            else if (PER_CHANNEL && e < 3 * D) src = decay + (tok * H + h) * D + (e - 2 * D);
-            else {
-                const int cc = blockIdx.x * LA_COLS + (e - (PER_CHANNEL ? 3 : 2) * D);
-                src = v + (tok * H + h) * V + min(cc, V - 1);
-            }
-            la_cp4(dst + idx, src);
+        for (int idx = threadIdx.x; idx < count * D; idx += blockDim.x) {
+            const int tt = idx / D, c = idx - tt * D;
+            const size_t at = ((size_t)(first + tt) * H + h) * D + c;
+            float* d = dst + tt * per_token + c;
+            la_cp4(d, q + at);
+            la_cp4(d + Dp, k + at);
+            if (PER_CHANNEL) la_cp4(d + 2 * Dp, decay + at);
+        }
+        for (int idx = threadIdx.x; idx < count * LA_COLS; idx += blockDim.x) {
+            const int tt = idx / LA_COLS, cc = idx % LA_COLS;
+            la_cp4(dst + tt * per_token + NA * Dp + cc,
+                   v + ((size_t)(first + tt) * H + h) * V + min(blockIdx.x * LA_COLS + cc, V - 1));
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -191,26 +233,43 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
         const int count = min(LA_TT, q_len - tile * LA_TT);
         for (int tt = 0; tt < count; ++tt) {
             const float* qs = base + tt * per_token;
-            const float* ks = qs + D;
-            const float* as = ks + D;
-            const float vj = qs[(PER_CHANNEL ? 3 : 2) * D + lane];
-            float partial = 0.f;
+            const float v0 = qs[NA * Dp + lane], v1 = qs[NA * Dp + 32 + lane];
+            float p0 = 0.f, p1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < LA_CPT; ++i) {
-                if (c_lo + i < c_hi) {
-                    const float a = PER_CHANNEL ? as[c_lo + i] : fixed;
-                    S[i] = fmaf(a, S[i], ks[c_lo + i] * vj);
-                    if (MODE == 1) P[i] *= a;
-                    else partial = fmaf(S[i], qs[c_lo + i], partial);
+            for (int i4 = 0; i4 < LA_CPT; i4 += 4) {
+                if (c_lo + i4 < c_hi) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(qs + c_lo + i4);
+                    const float4 k4 = *reinterpret_cast<const float4*>(qs + Dp + c_lo + i4);
+                    float4 a4 = make_float4(fixed, fixed, fixed, fixed);
+                    if (PER_CHANNEL) a4 = *reinterpret_cast<const float4*>(qs + 2 * Dp + c_lo + i4);
+                    const float qe[4] = {q4.x, q4.y, q4.z, q4.w}, ke[4] = {k4.x, k4.y, k4.z, k4.w}, ae[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if (c_lo + i4 + e < c_hi) {           // (the last channels of a head whose size is no multiple of 4)
+                            S0[i4 + e] = fmaf(ae[e], S0[i4 + e], ke[e] * v0);
+                            S1[i4 + e] = fmaf(ae[e], S1[i4 + e], ke[e] * v1);
+                            if (MODE == 1) P[i4 + e] *= ae[e];
+                            else {
+                                p0 = fmaf(S0[i4 + e], qe[e], p0);
+                                p1 = fmaf(S1[i4 + e], qe[e], p1);
+                            }
+                        }
+                    }
                 }
             }
             if (MODE == 1) continue;
-            red[(round * warps + warp) * 32 + lane] = partial;
+            float* mine = red + (size_t)(round * warps + warp) * 64;
+            mine[lane] = p0;
+            mine[32 + lane] = p1;
             __syncthreads();
-            if (warp == 0 && col) {
-                float o = red[(round * warps) * 32 + lane];
-                for (int w = 1; w < warps; ++w) o += red[(round * warps + w) * 32 + lane];
-                out[((size_t)(t0 + tile * LA_TT + tt) * H + h) * V + j] = o;
+            if (warp < 2) {                 // warp 0 adds the warps' sums of the first 32 columns in warp order, warp 1 (or 0) the others'
+                for (int half = warp; half < 2; half += min(warps, 2)) {
+                    const float* from = red + (size_t)(round * warps) * 64 + half * 32 + lane;
+                    float o = from[0];
+                    for (int w = 1; w < warps; ++w) o += from[(size_t)w * 64];
+                    if (half == 0 ? col0 : col1)
+                        out[((size_t)(t0 + tile * LA_TT + tt) * H + h) * V + (half == 0 ? j0 : j1)] = o;
+                }
             }
             round ^= 1;
         }
@@ -222,15 +281,19 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
 #pragma unroll
         for (int i = 0; i < LA_CPT; ++i)
             if (c_lo + i < c_hi) {
-                if (col) Ld[(size_t)(c_lo + i) * V + j] = S[i];
+                if (col0) Ld[(size_t)(c_lo + i) * V + j0] = S0[i];
+                if (col1) Ld[(size_t)(c_lo + i) * V + j1] = S1[i];
                 if (blockIdx.x == 0 && lane == 0) Ad[c_lo + i] = P[i];
             }
         return;
     }
-    if (col && (MODE == 0 || seg == nseg - 1)) {
+    if (MODE == 0 || seg == nseg - 1) {
 #pragma unroll
         for (int i = 0; i < LA_CPT; ++i)
-            if (c_lo + i < c_hi) Sg[(size_t)(c_lo + i) * V + j] = S[i];
+            if (c_lo + i < c_hi) {
+                if (col0) Sg[(size_t)(c_lo + i) * V + j0] = S0[i];
+                if (col1) Sg[(size_t)(c_lo + i) * V + j1] = S1[i];
+            }
     }
 }
 
@@ -264,14 +327,15 @@ WLLM_API int wllm_linattn_scan(const float* q, const float* k, const float* v, c
                                int requests, int H, int D, int V, int seg_len, int max_seg, float* seg_state, float* seg_decay,
                                cudaStream_t stream) {
     if (requests <= 0) return WLLM_OK;
-    if (H <= 0 || H > 65535 || requests > 65535 || D <= 0 || D > 32 * LA_CPT || V <= 0) return WLLM_BAD_SIZE;
+    if (H <= 0 || H > 65535 || requests > 65535 || D <= 0 || D > 16 * LA_CPT || V <= 0) return WLLM_BAD_SIZE;
     if (!decay && !head_decay) return WLLM_BAD_SIZE;
     const bool cut = seg_len > 0 && max_seg > 1;
     if (cut && (!seg_state || !seg_decay || (long long)requests * max_seg > 65535)) return WLLM_BAD_SIZE;
-    const int warps = (D + LA_CPT - 1) / LA_CPT;
-    const int cpt = (D + warps - 1) / warps;
+    const int most = (D + LA_CPT - 1) / LA_CPT;
+    const int cpt = (((D + most - 1) / most) + 3) & ~3;          // a multiple of 4, at most LA_CPT
+    const int warps = (D + cpt - 1) / cpt;
     const int vtiles = (V + LA_COLS - 1) / LA_COLS;
-    const size_t smem = ((size_t)2 * LA_TT * ((decay ? 3 : 2) * D + LA_COLS) + 2 * warps * 32) * sizeof(float);
+    const size_t smem = ((size_t)2 * LA_TT * ((decay ? 3 : 2) * ((D + 3) & ~3) + LA_COLS) + 2 * warps * 64) * sizeof(float);
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaSuccess;

@@ -269,3 +269,96 @@ WLLM_API int wllm_branch_norm(const void* a, int a_dtype, int a_parts, long long
     return wllm_launch(branch_norm_kernel, n, threads, 0, stream, a, a_dtype, a_parts, (size_t)a_stride, wa, b, b_dtype,
                        b_parts, (size_t)b_stride, wb, w_dtype, eps, center ? 1 : 0, factor, out, H);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// A block that norms behind its sublayers as well as in front, in one kernel a row:
+//     u   = a                                             (one branch), or
+//           factor * (rms(a) * wa + rms(b) * wb)          (two mixers side by side, each normed over the width)
+//     r  += norm_p(u) * wp                                (the norm behind the sublayer; center_p: layer norm)
+//     out = norm(r) * (offset + w)                        (the norm in front of the next sublayer, or the model's last)
+// The row lives in shared memory between the passes (H floats); every sum is a block sum in a fixed order.
+// With `rows` the residual is read at rows[i] and left as it is (the last norm at the places whose logits are wanted).
+// ---------------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void sandwich_norm_kernel(float* __restrict__ resid, const void* __restrict__ a, int a_dtype, int a_parts, size_t a_stride,
+                                     const void* __restrict__ wa, const void* __restrict__ b, int b_dtype, int b_parts,
+                                     size_t b_stride, const void* __restrict__ wb, float inner_eps, float factor,
+                                     const void* __restrict__ wp, int center_p, float eps_p, const void* __restrict__ w,
+                                     float offset, int center, float eps, int w_dtype, TO* __restrict__ out,
+                                     const int* __restrict__ rows, int H) {
+    extern __shared__ float row_s[];
+    __shared__ float scratch[32];
+    pdl_begin();
+    const int i = blockIdx.x;
+    const size_t row0 = (size_t)(rows ? rows[i] : i) * H;
+    float inv_a = 1.f, inv_b = 1.f;
+    if (wa) {
+        float ssa = 0.f, ssb = 0.f;
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float x = parts_at(a, a_dtype, a_parts, a_stride, row0 + c);
+            ssa += x * x;
+            if (b) { const float y = parts_at(b, b_dtype, b_parts, b_stride, row0 + c); ssb += y * y; }
+        }
+        inv_a = 1.0f / sqrtf(block_sum(ssa, scratch) / (float)H + inner_eps);
+        if (b) inv_b = 1.0f / sqrtf(block_sum(ssb, scratch) / (float)H + inner_eps);
+    }
+    float sum = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float u = parts_at(a, a_dtype, a_parts, a_stride, row0 + c);
+        if (wa) {
+            u = (u * inv_a) * any_at(wa, w_dtype, c);
+            if (b) u += (parts_at(b, b_dtype, b_parts, b_stride, row0 + c) * inv_b) * any_at(wb, w_dtype, c);
+            u *= factor;
+        }
+        row_s[c] = u;
+        sum += u;
+    }
+    float mean = center_p ? block_sum(sum, scratch) / (float)H : 0.f;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) ss += (row_s[c] - mean) * (row_s[c] - mean);
+    float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps_p);
+    sum = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float x = resid[row0 + c] + ((row_s[c] - mean) * inv) * any_at(wp, w_dtype, c);
+        if (!rows) resid[row0 + c] = x;
+        row_s[c] = x;
+        sum += x;
+    }
+    mean = center ? block_sum(sum, scratch) / (float)H : 0.f;
+    ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) ss += (row_s[c] - mean) * (row_s[c] - mean);
+    inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
+    TO* o = out + (size_t)i * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        o[c] = from_f32<TO>(((row_s[c] - mean) * inv) * (offset + any_at(w, w_dtype, c)));
+}
+
+// a, b: branch outputs [n, H] of either element type, or `parts` 32-bit slabs `stride` elements apart; wa null: a is taken as
+// it is (b, wb unused); all gains (wa, wb, wp, w) share one element type.
+WLLM_API int wllm_sandwich_norm(float* resid, const void* a, int a_dtype, int a_parts, long long a_stride, const void* wa,
+                                const void* b, int b_dtype, int b_parts, long long b_stride, const void* wb, float inner_eps,
+                                float factor, const void* wp, int center_p, float eps_p, const void* w, float offset, int center,
+                                float eps, int w_dtype, void* out, int out_dtype, const int* rows, int n, int H,
+                                cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (H <= 0 || H > 48 * 1024 || a_parts < 1 || (b && b_parts < 1) || (b && !wa)) return WLLM_BAD_SIZE;
+    if ((a_dtype != WLLM_BF16 && a_dtype != WLLM_F32) || (w_dtype != WLLM_BF16 && w_dtype != WLLM_F32) ||
+        (b && b_dtype != WLLM_BF16 && b_dtype != WLLM_F32))
+        return WLLM_BAD_DTYPE;
+    const size_t smem = (size_t)H * sizeof(float);
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(sandwich_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(sandwich_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        raised = true;
+    }
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define GO(TO) wllm_launch(sandwich_norm_kernel<TO>, n, threads, smem, stream, resid, a, a_dtype, a_parts, (size_t)a_stride, wa, b, \
+        b_dtype, b_parts, (size_t)b_stride, wb, inner_eps, factor, wp, center_p ? 1 : 0, eps_p, w, offset, center ? 1 : 0, eps, \
+        w_dtype, (TO*)out, rows, H)
+    if (out_dtype == WLLM_BF16) return GO(bf16);
+    if (out_dtype == WLLM_F32) return GO(float);
+#undef GO
+    return WLLM_BAD_DTYPE;
+}

@@ -165,6 +165,29 @@ def branch_norm(a, weight_a: torch.Tensor, out: torch.Tensor, eps: float, center
     return out
 
 
+def sandwich_norm(resid: torch.Tensor, a, out: torch.Tensor, post_weight: torch.Tensor, post_center: bool, post_eps: float,
+                  weight: torch.Tensor, offset: float, center: bool, eps: float, rows=None, gain_a=None, b=None, gain_b=None,
+                  inner_eps: float = 0.0, factor: float = 1.0) -> torch.Tensor:
+    """One kernel for a block that norms behind its sublayers too (csrc/norm.cu):
+        u = a, or factor * (rms(a) * gain_a + rms(b) * gain_b) when gain_a is given;
+        resid += norm(u) * post_weight  (post_center: with the mean taken off);  out = norm(resid) * (offset + weight).
+    `a`, `b`: (tensor [n, H] or float32 partial sums [S, n, H], S or 0).  With `rows` the residual is read at those rows
+    and left as it is."""
+    N, H = resid.shape
+    n = rows.shape[0] if rows is not None else N
+    _need_cuda(resid, a[0], out, post_weight, weight, rows, gain_a, gain_b, b[0] if b is not None else None)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous() and out.shape == (n, H)
+    gains = [g for g in (post_weight, weight, gain_a, gain_b) if g is not None]
+    assert all(g.shape == (H,) and g.is_contiguous() and g.dtype == weight.dtype for g in gains)
+    pa = _branch_args(a, N, H)
+    pb = _branch_args(b, N, H) if b is not None else (_ptr(None), _F32, 1, ctypes.c_longlong(0))
+    lib = load_family("norm")
+    _check(lib.wllm_sandwich_norm(_ptr(resid), *pa, _ptr(gain_a), *pb, _ptr(gain_b), c_float(inner_eps), c_float(factor),
+                                  _ptr(post_weight), 1 if post_center else 0, c_float(post_eps), _ptr(weight), c_float(offset),
+                                  1 if center else 0, c_float(eps), _dt(weight), _ptr(out), _dt(out),
+                                  _ptr(_int32(rows, "rows") if rows is not None else None), n, H, _stream()), "sandwich_norm")
+    return out
+
 def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor,
                   k_pages, v_pages, nq: int, nkv: int, hd: int, rot_dim: int, page_size: int, in_splits: int = 0,
                   pairing: str = "half", vd: int | None = None, unit_norm_eps: float | None = None) -> None:
@@ -684,14 +707,14 @@ LINATTN_MIN_SEGMENT = 32
 
 def linattn_segment_plan(max_q_len: int, requests_multi: int, heads: int, vdim: int) -> tuple:
     """(seg_len, max_seg) for the recurrence over a step whose longest portion has max_q_len tokens; (0, 1): every
-    request is walked in one go.  A walk is sequential in its tokens, and heads x tiles of 32 value columns x requests
+    request is walked in one go.  A walk is sequential in its tokens, and heads x tiles of 64 value columns x requests
     walks seldom fill the device; a long portion is therefore cut into segments that run side by side and are walked
-    twice (csrc/linear_attention.cu), as many as the device holds at once (about eight CTAs an SM), of at least
+    twice (csrc/linear_attention.cu), as many as the device holds at once (about three CTAs an SM), of at least
     LINATTN_MIN_SEGMENT tokens."""
     if max_q_len < LINATTN_SEGMENT_FROM:
         return 0, 1
-    walks = max(1, requests_multi) * heads * -(-vdim // 32)
-    wanted = (8 * sm_count()) // walks
+    walks = max(1, requests_multi) * heads * -(-vdim // 64)
+    wanted = (3 * sm_count()) // walks
     if wanted < 3:            # two segments walked twice are no shorter than one walk
         return 0, 1
     seg_len = max(LINATTN_MIN_SEGMENT, -(-(-(-max_q_len // wanted)) // 8) * 8)
@@ -752,4 +775,4 @@ __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "rope_k
            "attention_mma_decode", "attention_mma_prefill", "mma_head_dim_ok", "gemm_bf16_tc", "tc_gemm_ok",
            "tc_gemm_status",
            "gated_act", "gemm_f32", "linear", "project", "gated_linear", "split_plan", "branch_norm", "linattn_prepare",
-           "linattn_scan", "head_gate_norm"]
+           "linattn_scan", "head_gate_norm", "sandwich_norm"]

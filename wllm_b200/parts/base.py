@@ -102,6 +102,38 @@ class Partials:
         self.tensor, self.parts = tensor, tensor.shape[0]
 
 
+def branch_pair(branch) -> tuple:
+    """(tensor, parts) of a branch output, as the norm kernels take it."""
+    return (branch.tensor, branch.parts) if isinstance(branch, Partials) else (branch, 0)
+
+
+class MeanOfNormed:
+    """Two branch outputs whose sum is still to be taken: factor * (rms(a) * gain_a + rms(b) * gain_b), each normed over
+    the model width.  The norm that meets it works it out inside its own kernel; `materialize` does it alone."""
+
+    def __init__(self, a, gain_a, b, gain_b, eps: float, factor: float):
+        self.a, self.gain_a, self.b, self.gain_b, self.eps, self.factor = a, gain_a, b, gain_b, eps, factor
+
+    def materialize(self, ctx, name: str = "mean_of_normed") -> torch.Tensor:
+        from ..kernels import ops
+        pa, pb = branch_pair(self.a), branch_pair(self.b)
+        out = ctx.buffer(name, tuple(pa[0].shape[-2:]), torch.float32)
+        return ops.branch_norm(pa, self.gain_a, out, self.eps, center=False, factor=self.factor, b=pb, weight_b=self.gain_b)
+
+
+class NormedBranch:
+    """A branch output that is to pass a norm of its own before it joins the residual (a block that norms behind its
+    sublayers): `branch` is a tensor, `Partials` or `MeanOfNormed`, `norm` the norm part.  The next norm of the
+    residual does both in one kernel when it can; `materialize` runs the branch's norm alone."""
+
+    def __init__(self, branch, norm):
+        self.branch, self.norm = branch, norm
+
+    def materialize(self, ctx, name: str = "branch_normed") -> torch.Tensor:
+        inner = self.branch.materialize(ctx) if isinstance(self.branch, MeanOfNormed) else self.branch
+        return self.norm.branch(inner, ctx, name)
+
+
 def as_branch(product):
     """What ops.project returned, as a branch output: a tensor, or Partials."""
     tensor, parts = product
@@ -116,8 +148,10 @@ class Residual:
         self.stream = stream
         self.pending = None
 
-    def pending_args(self) -> tuple:
+    def pending_args(self, ctx=None) -> tuple:
         """(delta tensor or None, number of parts) for the norm kernel."""
+        if hasattr(self.pending, "materialize"):
+            self.pending = self.pending.materialize(ctx)
         if isinstance(self.pending, Partials):
             return self.pending.tensor, self.pending.parts
         return self.pending, 0

@@ -9,14 +9,14 @@ spec options: norm_in, mixer, norm_post, feed_forward (specs).
 
 'sandwich': a norm in front of and behind each sublayer,
     x = x + norm_mixer_out(mixer(norm_in(x)));  x = x + norm_ff_out(feed_forward(norm_post(x)))
-The norm behind a sublayer acts on the branch alone (`norm.branch`); its 32-bit result is what the next norm folds
-into the residual.  `feed_forward` may be None: the block then has its first sublayer only.
+The norm behind a sublayer acts on the branch alone; it is left pending on the residual as a `NormedBranch`, and the
+next norm of the residual runs it, the add and itself in one kernel (`norm.branch` does it alone where that cannot be).  `feed_forward` may be None: the block then has its first sublayer only.
 
 spec options: norm_in, mixer, norm_mixer_out, and norm_post, feed_forward, norm_ff_out (all three or none).
 """
 from __future__ import annotations
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheRef, Residual
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheRef, NormedBranch, Residual
 
 
 @BLOCKS.register("pre_norm")
@@ -63,6 +63,7 @@ class SandwichBlock:
         return self.mixer.cache_need()
 
     def __call__(self, residual: Residual, ctx, cache: CacheRef) -> None:
-        residual.pending = self.norm_mixer_out.branch(self.mixer(self.norm_in(residual, ctx), ctx, cache), ctx, "mixer_normed")
+        # the norm behind a sublayer is left to the next norm of the residual, which runs it inside its own kernel
+        residual.pending = NormedBranch(self.mixer(self.norm_in(residual, ctx), ctx, cache), self.norm_mixer_out)
         if self.feed_forward is not None:
-            residual.pending = self.norm_ff_out.branch(self.feed_forward(self.norm_post(residual, ctx), ctx), ctx, "ff_normed")
+            residual.pending = NormedBranch(self.feed_forward(self.norm_post(residual, ctx), ctx), self.norm_ff_out)

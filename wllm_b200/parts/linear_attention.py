@@ -25,7 +25,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import MIXERS, POSITIONS, CacheRef, KVNeed, ParamSpec, Partials, StateNeed, as_branch
+from .base import MIXERS, POSITIONS, CacheRef, KVNeed, MeanOfNormed, ParamSpec, StateNeed, as_branch
 
 
 @MIXERS.register("linear_attention")
@@ -34,8 +34,8 @@ class LinearAttention:
 
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.heads, self.dim, self.vdim = int(spec.num_heads), int(spec.key_dim), int(spec.value_dim)
-        if self.dim > 512:
-            raise ValueError(f"key_dim {self.dim}: the recurrence kernel holds up to 512 key channels a head")
+        if self.dim > 256:
+            raise ValueError(f"key_dim {self.dim}: the recurrence kernel holds up to 256 key channels a head")
         self.eps = float(spec.eps)
         self.q_scale, self.k_scale = float(spec.options.get("q_scale", 1.0)), float(spec.options.get("k_scale", 1.0))
         self.hidden_size, self.model_dtype = hidden_size, model_dtype
@@ -194,9 +194,5 @@ class ParallelMean:
         fused, parts = ops.project(x, self.w_in, lambda name, shape, dt: ctx.buffer("parallel_in_" + name, shape, dt))
         a = self.left.mix(fused, parts, 0, ctx, self._side(cache, "left"))
         b = self.right.mix(fused, parts, self.left_width, ctx, self._side(cache, "right"))
-        out = ctx.buffer("parallel_mean", (x.shape[0], self.hidden_size), torch.float32)
-
-        def pair(branch):
-            return (branch.tensor, branch.parts) if isinstance(branch, Partials) else (branch, 0)
-        return ops.branch_norm(pair(a), self.gain_left, out, self.eps, center=False, factor=0.5, b=pair(b),
-                               weight_b=self.gain_right)
+        # half the sum of the two normed outputs is taken by whoever reads the branch (the next norm's kernel)
+        return MeanOfNormed(a, self.gain_left, b, self.gain_right, self.eps, 0.5)

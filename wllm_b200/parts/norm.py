@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import NORMS, ParamSpec, Partials, Residual
+from .base import NORMS, MeanOfNormed, NormedBranch, ParamSpec, Partials, Residual, branch_pair
 
 
 @NORMS.register("rmsnorm")
@@ -37,29 +37,44 @@ class RMSNorm:
 
     def __call__(self, residual: Residual, ctx) -> torch.Tensor:
         out = ctx.buffer("normed", (residual.stream.shape[0], self.hidden_size), self.model_dtype)
-        delta, parts = residual.pending_args()
-        if self.center:
-            ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, delta_splits=parts, center=True)
-        else:
-            ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, delta_splits=parts)
+        self._run(residual, ctx, out, None)
         residual.pending = None
         return out
 
     def rows(self, residual: Residual, rows: torch.Tensor, ctx) -> torch.Tensor:
         out = torch.empty((rows.shape[0], self.hidden_size), dtype=self.model_dtype, device=rows.device)
-        delta, parts = residual.pending_args()
-        if self.center:
-            ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, rows=rows, delta_splits=parts,
-                        center=True)
-        else:
-            ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, rows=rows, delta_splits=parts)
+        self._run(residual, ctx, out, rows)
         return out
+
+    def _run(self, residual: Residual, ctx, out, rows) -> None:
+        pending = residual.pending
+        if isinstance(pending, NormedBranch) and self._fusable(pending):
+            # the branch's own norm, the add and this norm in one kernel; two mixers' outputs are normed and averaged there too
+            post, inner, more = pending.norm, pending.branch, {}
+            if isinstance(inner, MeanOfNormed):
+                more = dict(gain_a=inner.gain_a, b=branch_pair(inner.b), gain_b=inner.gain_b, inner_eps=inner.eps, factor=inner.factor)
+                inner = inner.a
+            ops.sandwich_norm(residual.stream, branch_pair(inner), out, post.weight, post.center, post.eps, self.weight,
+                              self.offset, self.center, self.eps, rows=rows, **more)
+            return
+        delta, parts = residual.pending_args(ctx)
+        extra = {"center": True} if self.center else {}
+        if rows is not None:
+            extra["rows"] = rows
+        ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, delta_splits=parts, **extra)
+
+    def _fusable(self, pending: NormedBranch) -> bool:
+        post = pending.norm
+        if not isinstance(post, RMSNorm) or post.offset or post.weight.dtype != self.weight.dtype or self.hidden_size > 48 * 1024:
+            return False
+        inner = pending.branch
+        return not isinstance(inner, MeanOfNormed) or inner.gain_a.dtype == self.weight.dtype == inner.gain_b.dtype
 
     def branch(self, branch, ctx, name: str = "branch_normed") -> torch.Tensor:
         """The norm of a branch output (a tensor [n, hidden] or `Partials`), 32-bit; a gain of 1 + w is not offered here."""
         if self.offset:
             raise ValueError("the norm of a branch takes its gain as stored (unit_offset is for norms of the residual)")
-        pair = (branch.tensor, branch.parts) if isinstance(branch, Partials) else (branch, 0)
+        pair = branch_pair(branch)
         out = ctx.buffer(name, (pair[0].shape[-2], self.hidden_size), torch.float32)
         return ops.branch_norm(pair, self.weight, out, self.eps, center=self.center)
 
