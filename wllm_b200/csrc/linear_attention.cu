@@ -16,7 +16,7 @@
 //   wllm_linattn_scan       the recurrence.  Grid (tiles of 64 value columns, heads, requests); a lane owns two
 //                           columns of S, a warp a run of at most 16 key channels of them, in registers.  Tokens
 //                           arrive in tiles of 8 through a two-stage cp.async ring; the warps' partial dot products of a
-//                           token meet in shared memory and are added in warp order.  Long portions of prompts are cut
+//                           tile's tokens meet in shared memory once a tile and are added in warp order.  Long portions of prompts are cut
 //                           into segments that are walked side by side: from zero for their local end states, which a
 //                           small kernel chains into start states, and once more from those for the outputs.
 //   wllm_head_gate_norm     per head: o / sqrt(mean(o^2) + eps) [* w] * silu(g), rounded once to the matrix type
@@ -34,11 +34,13 @@ __device__ __forceinline__ float la_in(const void* p, int dtype, int parts, size
 }
 
 // ---------------------------------------------------------------------------------------------------
-// prepare: grid (tiles of PREP_TT tokens, heads), 128 threads
+// prepare: grid (tiles of TT tokens, heads), 128 threads
 // ---------------------------------------------------------------------------------------------------
-constexpr int PREP_TT = 8;       // tokens of a CTA: the head's slab of the low-rank matrix is read once for all of them
 constexpr int PREP_RK = 32;      // columns of the low-rank map taken at a time
 
+// TT tokens a CTA: the head's slab of the low-rank matrix is read once for all of them (prompts: 8); a step of few
+// tokens takes one token a CTA, so that tokens x heads CTAs share the work.
+template <int TT>
 __global__ void __launch_bounds__(128)
 linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_stride, int parts, size_t part_stride,
                        int q_off, int k_off, int v_off, int a_off, int n, int H, int D, int V, int rank,
@@ -47,43 +49,47 @@ linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_str
                        int w_dtype, float inv_tau, float* __restrict__ q, float* __restrict__ k,
                        float* __restrict__ v, float* __restrict__ decay) {
     __shared__ float w_s[128][PREP_RK + 1];      // [channel of the chunk][column], padded against bank conflicts
-    __shared__ float low_s[PREP_TT][PREP_RK];
+    __shared__ float low_s[TT][PREP_RK];
     pdl_begin();
-    const int t_lo = blockIdx.x * PREP_TT, h = blockIdx.y;
-    const int count = min(PREP_TT, n - t_lo);
-    const int half = rot_dim >> 1;
-    for (int tt = 0; tt < count; ++tt) {
-        const int t = t_lo + tt;
-        const size_t row = (size_t)t * row_stride;
-        const float pos = (float)positions[t];
-        for (int which = 0; which < 2; ++which) {
-            const int off = (which ? k_off : q_off) + h * D;
-            float* dst = (which ? k : q) + ((size_t)t * H + h) * D;
-            const float scale = which ? k_scale : q_scale;
-            for (int j = threadIdx.x; j < half; j += blockDim.x) {
-                float sn, cs, y1, y2;
-                sincosf(pos * inv_freq[j], &sn, &cs);
-                rotate_pair(la_in(fused, in_dtype, parts, part_stride, row + off + j),
-                            la_in(fused, in_dtype, parts, part_stride, row + off + j + half), sn, cs, y1, y2);
-                dst[j] = y1 * scale;
-                dst[j + half] = y2 * scale;
-            }
-            for (int c = rot_dim + threadIdx.x; c < D; c += blockDim.x)
-                dst[c] = la_in(fused, in_dtype, parts, part_stride, row + off + c) * scale;
+    const int t_lo = blockIdx.x * TT, h = blockIdx.y;
+    const int count = min(TT, n - t_lo);
+    const int half = rot_dim >> 1, rest = D - rot_dim;
+    // q and k: the rotated pairs, then the channels behind them; v: a copy.  One flat loop each over (token, element),
+    // so that a thread's loads do not wait for one another.
+    for (int which = 0; which < 2; ++which) {
+        const int off = (which ? k_off : q_off) + h * D;
+        float* base = which ? k : q;
+        const float scale = which ? k_scale : q_scale;
+        for (int idx = threadIdx.x; idx < count * half; idx += blockDim.x) {
+            const int tt = idx / half, j = idx - tt * half, t = t_lo + tt;
+            const size_t row = (size_t)t * row_stride + off;
+            float sn, cs, y1, y2;
+            sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+            rotate_pair(la_in(fused, in_dtype, parts, part_stride, row + j),
+                        la_in(fused, in_dtype, parts, part_stride, row + j + half), sn, cs, y1, y2);
+            float* dst = base + ((size_t)t * H + h) * D;
+            dst[j] = y1 * scale;
+            dst[j + half] = y2 * scale;
         }
-        for (int c = threadIdx.x; c < V; c += blockDim.x)
-            v[((size_t)t * H + h) * V + c] = la_in(fused, in_dtype, parts, part_stride, row + v_off + h * V + c);
+        for (int idx = threadIdx.x; idx < count * rest; idx += blockDim.x) {
+            const int tt = idx / rest, c = rot_dim + idx - tt * rest, t = t_lo + tt;
+            base[((size_t)t * H + h) * D + c] = la_in(fused, in_dtype, parts, part_stride, (size_t)t * row_stride + off + c) * scale;
+        }
+    }
+    for (int idx = threadIdx.x; idx < count * V; idx += blockDim.x) {
+        const int tt = idx / V, c = idx - tt * V, t = t_lo + tt;
+        v[((size_t)t * H + h) * V + c] = la_in(fused, in_dtype, parts, part_stride, (size_t)t * row_stride + v_off + h * V + c);
     }
     if (a_off < 0) return;
-    // z[token][channel] = b2[channel] + sum_r low[token][r] * w2[channel][r]: a thread a channel, PREP_TT sums each;
+    // z[token][channel] = b2[channel] + sum_r low[token][r] * w2[channel][r]: a thread a channel, TT sums each;
     // the sum over r runs in ascending order whatever the tiling
     for (int c0 = 0; c0 < D; c0 += 128) {
         const int c = c0 + threadIdx.x;
         const size_t ch = (size_t)h * D + min(c, D - 1);
-        float z[PREP_TT];
+        float z[TT];
         const float bias = la_any(b2, w_dtype, ch);
 #pragma unroll
-        for (int tt = 0; tt < PREP_TT; ++tt) z[tt] = bias;
+        for (int tt = 0; tt < TT; ++tt) z[tt] = bias;
         for (int r0 = 0; r0 < rank; r0 += PREP_RK) {
             const int rk = min(PREP_RK, rank - r0);
             __syncthreads();
@@ -91,7 +97,7 @@ linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_str
                 const int cc = idx / PREP_RK, r = idx % PREP_RK;
                 w_s[cc][r] = (c0 + cc < D && r < rk) ? la_any(w2, w_dtype, ((size_t)h * D + c0 + cc) * rank + r0 + r) : 0.f;
             }
-            for (int idx = threadIdx.x; idx < PREP_TT * PREP_RK; idx += blockDim.x) {
+            for (int idx = threadIdx.x; idx < TT * PREP_RK; idx += blockDim.x) {
                 const int tt = idx / PREP_RK, r = idx % PREP_RK;
                 low_s[tt][r] = (tt < count && r < rk)
                     ? la_in(fused, in_dtype, parts, part_stride, (size_t)(t_lo + tt) * row_stride + a_off + r0 + r) : 0.f;
@@ -101,12 +107,12 @@ linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_str
             for (int r = 0; r < PREP_RK; ++r) {
                 const float w = w_s[threadIdx.x][r];
 #pragma unroll
-                for (int tt = 0; tt < PREP_TT; ++tt) z[tt] = fmaf(low_s[tt][r], w, z[tt]);
+                for (int tt = 0; tt < TT; ++tt) z[tt] = fmaf(low_s[tt][r], w, z[tt]);
             }
         }
         if (c < D) {
 #pragma unroll
-            for (int tt = 0; tt < PREP_TT; ++tt) {
+            for (int tt = 0; tt < TT; ++tt) {
                 if (tt >= count) break;
                 // log(sigmoid(z)) = min(z, 0) - log(1 + e^-|z|), exact at both ends
                 const float log_sig = fminf(z[tt], 0.f) - log1pf(expf(-fabsf(z[tt])));
@@ -126,9 +132,12 @@ WLLM_API int wllm_linattn_prepare(const void* fused, int in_dtype, int row_strid
     if (a_off >= 0 && (rank <= 0 || !(tau > 0.f) || !w2 || !b2 || !decay)) return WLLM_BAD_SIZE;
     if ((in_dtype != WLLM_BF16 && in_dtype != WLLM_F32) || (a_off >= 0 && w_dtype != WLLM_BF16 && w_dtype != WLLM_F32))
         return WLLM_BAD_DTYPE;
-    return wllm_launch(linattn_prepare_kernel, dim3((n + PREP_TT - 1) / PREP_TT, H), 128, 0, stream, fused,
-                       in_dtype, row_stride, parts, (size_t)part_stride, q_off, k_off, v_off, a_off, n, H, D, V, rank, positions,
-                       inv_freq, rot_dim, q_scale, k_scale, w2, b2, w_dtype, a_off >= 0 ? 1.0f / tau : 0.f, q, k, v, decay);
+#define PREP(TT) wllm_launch(linattn_prepare_kernel<TT>, dim3((n + TT - 1) / TT, H), 128, 0, stream, fused, \
+        in_dtype, row_stride, parts, (size_t)part_stride, q_off, k_off, v_off, a_off, n, H, D, V, rank, positions, \
+        inv_freq, rot_dim, q_scale, k_scale, w2, b2, w_dtype, a_off >= 0 ? 1.0f / tau : 0.f, q, k, v, decay)
+    if ((long long)n * H >= 2048) return PREP(8);
+    return PREP(1);
+#undef PREP
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -182,7 +191,7 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
     const int Dp = (D + 3) & ~3, NA = PER_CHANNEL ? 3 : 2;
     const int per_token = NA * Dp + LA_COLS;
     float* stage0 = la_smem;
-    float* red = la_smem + 2 * LA_TT * per_token;             // [2][warps][64]
+    float* red = la_smem + 2 * LA_TT * per_token;             // [2][warps][LA_TT][64]
 
     float S0[LA_CPT], S1[LA_CPT], P[LA_CPT];
     float* Sg = state + (((size_t)slot * H + h) * D) * V;
@@ -231,49 +240,62 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
         __syncthreads();
         const float* base = stage0 + (size_t)stage * LA_TT * per_token;
         const int count = min(LA_TT, q_len - tile * LA_TT);
-        for (int tt = 0; tt < count; ++tt) {
-            const float* qs = base + tt * per_token;
-            const float v0 = qs[NA * Dp + lane], v1 = qs[NA * Dp + 32 + lane];
-            float p0 = 0.f, p1 = 0.f;
+        float p0[LA_TT], p1[LA_TT];          // this warp's share of the tile's outputs, two columns
 #pragma unroll
-            for (int i4 = 0; i4 < LA_CPT; i4 += 4) {
-                if (c_lo + i4 < c_hi) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(qs + c_lo + i4);
-                    const float4 k4 = *reinterpret_cast<const float4*>(qs + Dp + c_lo + i4);
-                    float4 a4 = make_float4(fixed, fixed, fixed, fixed);
-                    if (PER_CHANNEL) a4 = *reinterpret_cast<const float4*>(qs + 2 * Dp + c_lo + i4);
-                    const float qe[4] = {q4.x, q4.y, q4.z, q4.w}, ke[4] = {k4.x, k4.y, k4.z, k4.w}, ae[4] = {a4.x, a4.y, a4.z, a4.w};
+        for (int tt = 0; tt < LA_TT; ++tt) {
+            p0[tt] = p1[tt] = 0.f;
+            if (tt < count) {
+                const float* qs = base + tt * per_token;
+                const float v0 = qs[NA * Dp + lane], v1 = qs[NA * Dp + 32 + lane];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        if (c_lo + i4 + e < c_hi) {           // (the last channels of a head whose size is no multiple of 4)
-                            S0[i4 + e] = fmaf(ae[e], S0[i4 + e], ke[e] * v0);
-                            S1[i4 + e] = fmaf(ae[e], S1[i4 + e], ke[e] * v1);
-                            if (MODE == 1) P[i4 + e] *= ae[e];
-                            else {
-                                p0 = fmaf(S0[i4 + e], qe[e], p0);
-                                p1 = fmaf(S1[i4 + e], qe[e], p1);
+                for (int i4 = 0; i4 < LA_CPT; i4 += 4) {
+                    if (c_lo + i4 < c_hi) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(qs + c_lo + i4);
+                        const float4 k4 = *reinterpret_cast<const float4*>(qs + Dp + c_lo + i4);
+                        float4 a4 = make_float4(fixed, fixed, fixed, fixed);
+                        if (PER_CHANNEL) a4 = *reinterpret_cast<const float4*>(qs + 2 * Dp + c_lo + i4);
+                        const float qe[4] = {q4.x, q4.y, q4.z, q4.w}, ke[4] = {k4.x, k4.y, k4.z, k4.w}, ae[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (c_lo + i4 + e < c_hi) {           // (the last channels of a head whose size is no multiple of 4)
+                                S0[i4 + e] = fmaf(ae[e], S0[i4 + e], ke[e] * v0);
+                                S1[i4 + e] = fmaf(ae[e], S1[i4 + e], ke[e] * v1);
+                                if (MODE == 1) P[i4 + e] *= ae[e];
+                                else {
+                                    p0[tt] = fmaf(S0[i4 + e], qe[e], p0[tt]);
+                                    p1[tt] = fmaf(S1[i4 + e], qe[e], p1[tt]);
+                                }
                             }
                         }
                     }
                 }
             }
-            if (MODE == 1) continue;
-            float* mine = red + (size_t)(round * warps + warp) * 64;
-            mine[lane] = p0;
-            mine[32 + lane] = p1;
-            __syncthreads();
-            if (warp < 2) {                 // warp 0 adds the warps' sums of the first 32 columns in warp order, warp 1 (or 0) the others'
-                for (int half = warp; half < 2; half += min(warps, 2)) {
-                    const float* from = red + (size_t)(round * warps) * 64 + half * 32 + lane;
-                    float o = from[0];
-                    for (int w = 1; w < warps; ++w) o += from[(size_t)w * 64];
-                    if (half == 0 ? col0 : col1)
-                        out[((size_t)(t0 + tile * LA_TT + tt) * H + h) * V + (half == 0 ? j0 : j1)] = o;
-                }
-            }
-            round ^= 1;
         }
-        if (MODE == 1) __syncthreads();       // the stage is read to its end before the tile after next lands in it
+        if (MODE == 1) {
+            __syncthreads();       // the stage is read to its end before the tile after next lands in it
+            continue;
+        }
+        // the warps' sums meet once a tile: red[round][warp][token][64]; then warp w adds up the tokens w, w + warps, ..
+        // in warp order (the sum of a token depends on nothing but the token)
+        float* mine = red + ((size_t)(round * warps + warp) * LA_TT) * 64;
+#pragma unroll
+        for (int tt = 0; tt < LA_TT; ++tt) {
+            mine[tt * 64 + lane] = p0[tt];
+            mine[tt * 64 + 32 + lane] = p1[tt];
+        }
+        __syncthreads();           // (also: every warp has read the stage to its end)
+        for (int tt = warp; tt < count; tt += warps) {
+            const float* from = red + ((size_t)(round * warps) * LA_TT + tt) * 64 + lane;
+            float o0 = from[0], o1 = from[32];
+            for (int w = 1; w < warps; ++w) {
+                o0 += from[(size_t)w * LA_TT * 64];
+                o1 += from[(size_t)w * LA_TT * 64 + 32];
+            }
+            float* orow = out + ((size_t)(t0 + tile * LA_TT + tt) * H + h) * V;
+            if (col0) orow[j0] = o0;
+            if (col1) orow[j1] = o1;
+        }
+        round ^= 1;
     }
     if (MODE == 1) {
         float* Ld = seg_state + (((size_t)(r * max_seg + seg + 1) * H + h) * D) * V;
@@ -335,7 +357,7 @@ WLLM_API int wllm_linattn_scan(const float* q, const float* k, const float* v, c
     const int cpt = (((D + most - 1) / most) + 3) & ~3;          // a multiple of 4, at most LA_CPT
     const int warps = (D + cpt - 1) / cpt;
     const int vtiles = (V + LA_COLS - 1) / LA_COLS;
-    const size_t smem = ((size_t)2 * LA_TT * ((decay ? 3 : 2) * ((D + 3) & ~3) + LA_COLS) + 2 * warps * 64) * sizeof(float);
+    const size_t smem = ((size_t)2 * LA_TT * ((decay ? 3 : 2) * ((D + 3) & ~3) + LA_COLS) + 2 * warps * LA_TT * 64) * sizeof(float);
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaSuccess;

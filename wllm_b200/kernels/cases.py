@@ -8,6 +8,7 @@ print what it achieved against the roofline.  The same command under `ncu` gives
     python -m wllm_b200.kernels.cases sampling --rows 8 --vocab 256000 --top-k 50 --top-p 0.9
     python -m wllm_b200.kernels.cases gemm-f32 --m 16 --n 49152 --k 3072
     python -m wllm_b200.kernels.cases attention-f32 --requests 16 --context 6000 --tokens 1 --heads 16 --kv-heads 16
+    python -m wllm_b200.kernels.cases recurrence --requests 1 --tokens 2048 --heads 8 --dim 128 --vdim 256
 
 Operands are larger than L2 where the case is bound by memory (several weight copies are cycled), so the
 figures are DRAM figures.  Peaks: MEASURED_PEAKS.json at the repository root when present, else the fallback
@@ -205,6 +206,34 @@ def sampling(args) -> None:
           f"({passes * rows * V * 4 / ms / 1e6:.0f} GB/s out of L2)")
 
 
+def recurrence(args) -> None:
+    """The decayed-state recurrence of linear attention (csrc/linear_attention.cu) over `requests` portions of `tokens`
+    tokens each (1: a decode step), decay per key channel or per head."""
+    R, T, H, D, V = args.requests, args.tokens, args.heads, args.dim, args.vdim
+    n = R * T
+    g = torch.Generator(device=DEV).manual_seed(1)
+    q, k = (torch.randn(n, H * D, device=DEV, generator=g) for _ in range(2))
+    v = torch.randn(n, H * V, device=DEV, generator=g)
+    decay = None if args.per_head else torch.rand(n, H * D, device=DEV, generator=g) * 0.1 + 0.9
+    head_decay = torch.full((H,), 0.97, device=DEV) if args.per_head else None
+    state = torch.zeros(R, H, D, V, device=DEV)
+    out = torch.empty(n, H * V, device=DEV)
+    starts = torch.arange(R, dtype=torch.int32, device=DEV) * T
+    lens = torch.full((R,), T, dtype=torch.int32, device=DEV)
+    slots = torch.arange(R, dtype=torch.int32, device=DEV)
+    seg_len, max_seg = (0, 1) if args.no_segments else ops.linattn_segment_plan(T, R if T > 1 else 0, H, V)
+    seg_state = torch.empty(R * max_seg * H * D * V, device=DEV)
+    seg_decay = torch.empty(R * max_seg * H * D, device=DEV)
+    ms = timed(lambda: ops.linattn_scan(q, k, v, decay, head_decay, state, out, starts, lens, slots, H, D, V, seg_len, max_seg,
+                                        seg_state, seg_decay), args.iters)
+    hbm, _, src = peaks()
+    moved = n * ((3 if decay is not None else 2) * H * D + 2 * H * V) * 4 + 2 * R * H * D * V * 4
+    fma = 3.0 * n * H * D * V * (2 if max_seg > 1 else 1)
+    print(f"recurrence requests={R} tokens={T} heads={H} dim={D} vdim={V} segments={max_seg}x{seg_len}: {ms * 1e3:.1f} us, "
+          f"{moved / 1e6:.1f} MB that must move ({moved / ms / 1e6:.0f} GB/s, {moved / ms / 1e6 / hbm:.3f} of {src} copy bandwidth), "
+          f"{fma / ms / 1e9:.2f} T 32-bit multiply-adds and multiplies a second")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m wllm_b200.kernels.cases", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -230,6 +259,14 @@ def main(argv=None) -> int:
         a.add_argument("--page-size", type=int, default=64)
         a.add_argument("--no-share", action="store_true", help="prefill: never share a heavy tile between two CTAs")
         a.add_argument("--walk", action="store_true", help="attention-f32: one warp per row even where chunks would be split or rows tiled")
+    rc = sub.add_parser("recurrence")
+    rc.add_argument("--requests", type=int, default=1)
+    rc.add_argument("--tokens", type=int, default=2048)
+    rc.add_argument("--heads", type=int, default=8)
+    rc.add_argument("--dim", type=int, default=128)
+    rc.add_argument("--vdim", type=int, default=256)
+    rc.add_argument("--per-head", action="store_true", help="one decay per head (retention) instead of one per key channel")
+    rc.add_argument("--no-segments", action="store_true", help="walk every portion in one go")
     sm = sub.add_parser("sampling")
     sm.add_argument("--rows", type=int, default=8)
     sm.add_argument("--vocab", type=int, default=256000)
@@ -251,6 +288,8 @@ def main(argv=None) -> int:
         attention_f32(args)
     elif args.case == "sampling":
         sampling(args)
+    elif args.case == "recurrence":
+        recurrence(args)
     else:
         attention(args, decode=args.case == "attention-decode")
     return 0

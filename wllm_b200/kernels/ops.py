@@ -709,12 +709,12 @@ def linattn_segment_plan(max_q_len: int, requests_multi: int, heads: int, vdim: 
     """(seg_len, max_seg) for the recurrence over a step whose longest portion has max_q_len tokens; (0, 1): every
     request is walked in one go.  A walk is sequential in its tokens, and heads x tiles of 64 value columns x requests
     walks seldom fill the device; a long portion is therefore cut into segments that run side by side and are walked
-    twice (csrc/linear_attention.cu), as many as the device holds at once (about three CTAs an SM), of at least
+    twice (csrc/linear_attention.cu), as many as the device holds at once (two CTAs an SM), of at least
     LINATTN_MIN_SEGMENT tokens."""
     if max_q_len < LINATTN_SEGMENT_FROM:
         return 0, 1
     walks = max(1, requests_multi) * heads * -(-vdim // 64)
-    wanted = (3 * sm_count()) // walks
+    wanted = (2 * sm_count()) // walks
     if wanted < 3:            # two segments walked twice are no shorter than one walk
         return 0, 1
     seg_len = max(LINATTN_MIN_SEGMENT, -(-(-(-max_q_len // wanted)) // 8) * 8)
