@@ -48,8 +48,7 @@ linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_str
                        float q_scale, float k_scale, const void* __restrict__ w2, const void* __restrict__ b2,
                        int w_dtype, float inv_tau, float* __restrict__ q, float* __restrict__ k,
                        float* __restrict__ v, float* __restrict__ decay) {
-    __shared__ float w_s[128][PREP_RK + 1];      // [channel of the chunk][column], padded against bank conflicts
-    __shared__ float low_s[TT][PREP_RK];
+    __shared__ __align__(16) float low_s[PREP_RK][TT];      // the tokens' low-rank vectors, a run of PREP_RK columns at a time
     pdl_begin();
     const int t_lo = blockIdx.x * TT, h = blockIdx.y;
     const int count = min(TT, n - t_lo);
@@ -81,8 +80,10 @@ linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_str
         v[((size_t)t * H + h) * V + c] = la_in(fused, in_dtype, parts, part_stride, (size_t)t * row_stride + v_off + h * V + c);
     }
     if (a_off < 0) return;
-    // z[token][channel] = b2[channel] + sum_r low[token][r] * w2[channel][r]: a thread a channel, TT sums each;
-    // the sum over r runs in ascending order whatever the tiling
+    // z[token][channel] = b2[channel] + sum_r low[token][r] * w2[channel][r]: a thread a channel, TT sums each; the
+    // thread takes PREP_RK of its channel's weights into registers at a time (16-byte loads where the rows allow), the
+    // tokens' low-rank vectors come from shared memory.  The sum over r runs in ascending order whatever the tiling.
+    const bool vec = ((uintptr_t)w2 & 15) == 0 && rank % 8 == 0;
     for (int c0 = 0; c0 < D; c0 += 128) {
         const int c = c0 + threadIdx.x;
         const size_t ch = (size_t)h * D + min(c, D - 1);
@@ -93,21 +94,45 @@ linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_str
         for (int r0 = 0; r0 < rank; r0 += PREP_RK) {
             const int rk = min(PREP_RK, rank - r0);
             __syncthreads();
-            for (int idx = threadIdx.x; idx < 128 * PREP_RK; idx += blockDim.x) {
-                const int cc = idx / PREP_RK, r = idx % PREP_RK;
-                w_s[cc][r] = (c0 + cc < D && r < rk) ? la_any(w2, w_dtype, ((size_t)h * D + c0 + cc) * rank + r0 + r) : 0.f;
-            }
             for (int idx = threadIdx.x; idx < TT * PREP_RK; idx += blockDim.x) {
-                const int tt = idx / PREP_RK, r = idx % PREP_RK;
-                low_s[tt][r] = (tt < count && r < rk)
+                const int r = idx / TT, tt = idx % TT;
+                low_s[r][tt] = (tt < count && r < rk)
                     ? la_in(fused, in_dtype, parts, part_stride, (size_t)(t_lo + tt) * row_stride + a_off + r0 + r) : 0.f;
             }
-            __syncthreads();
-#pragma unroll 8
-            for (int r = 0; r < PREP_RK; ++r) {
-                const float w = w_s[threadIdx.x][r];
+            float wr[PREP_RK];
+            if (vec && rk == PREP_RK) {
+                if (w_dtype == WLLM_BF16) {
+                    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(w2) + ch * rank + r0);
+                    uint4 raw[PREP_RK / 8];
 #pragma unroll
-                for (int tt = 0; tt < TT; ++tt) z[tt] = fmaf(low_s[tt][r], w, z[tt]);
+                    for (int u = 0; u < PREP_RK / 8; ++u) raw[u] = src[u];
+#pragma unroll
+                    for (int u = 0; u < PREP_RK / 8; ++u) {
+                        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 f = __bfloat1622float2(h2[e]);
+                            wr[u * 8 + 2 * e] = f.x;
+                            wr[u * 8 + 2 * e + 1] = f.y;
+                        }
+                    }
+                } else {
+                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w2) + ch * rank + r0);
+#pragma unroll
+                    for (int u = 0; u < PREP_RK / 4; ++u) {
+                        const float4 f = src[u];
+                        wr[u * 4] = f.x; wr[u * 4 + 1] = f.y; wr[u * 4 + 2] = f.z; wr[u * 4 + 3] = f.w;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < PREP_RK; ++r) wr[r] = r < rk ? la_any(w2, w_dtype, ch * rank + r0 + r) : 0.f;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int r = 0; r < PREP_RK; ++r) {
+#pragma unroll
+                for (int tt = 0; tt < TT; ++tt) z[tt] = fmaf(low_s[r][tt], wr[r], z[tt]);
             }
         }
         if (c < D) {

@@ -27,8 +27,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
                                      TO* __restrict__ q_out, int q_stride, const int* __restrict__ positions,
                                      const int* __restrict__ slots, const float* __restrict__ inv_freq,
                                      TO* __restrict__ k_pages, TO* __restrict__ v_pages, int nq, int nkv, int hd,
-                                     int rot_dim, int page_size, int interleaved, int vd, int unit_norm, float norm_eps) {
-    extern __shared__ float head_buf[];      // unit_norm: [hd] the rotated head, then 32 floats for the reduction
+                                     int rot_dim, int page_size, int interleaved, int vd) {
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const int slot = slots ? slots[t] : -1;
@@ -68,29 +67,6 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
             for (int c = threadIdx.x; c < vd; c += blockDim.x) dst[c] = from_f32<TO>(in(c));
             continue;
         }
-        if (unit_norm) {         // the same turn, kept in 32-bit until the head's mean square is known
-            float ss = 0.f;
-            for (int j = threadIdx.x; j < half; j += blockDim.x) {
-                float sn = s0, cs = c0;
-                if (j != (int)threadIdx.x) sincosf(pos * inv_freq[j], &sn, &cs);
-                const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
-                float y1, y2;
-                rotate_pair(in(ia), in(ib), sn, cs, y1, y2);
-                head_buf[ia] = y1;
-                head_buf[ib] = y2;
-                ss += y1 * y1 + y2 * y2;
-            }
-            for (int c = rot_dim + threadIdx.x; c < hd; c += blockDim.x) {
-                const float y = in(c);
-                head_buf[c] = y;
-                ss += y * y;
-            }
-            ss = block_sum(ss, head_buf + hd);
-            const float inv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
-            for (int c = threadIdx.x; c < hd; c += blockDim.x) dst[c] = from_f32<TO>(head_buf[c] * inv);
-            __syncthreads();     // the buffer is free for the next head
-            continue;
-        }
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
             float sn = s0, cs = c0;
             if (j != (int)threadIdx.x) sincosf(pos * inv_freq[j], &sn, &cs);
@@ -102,6 +78,88 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
             dst[ib] = from_f32<TO>(y2);
         }
         for (int c = rot_dim + threadIdx.x; c < hd; c += blockDim.x) dst[c] = from_f32<TO>(in(c));
+    }
+}
+
+// Heads that are divided by their root mean square after the turn: a warp a head (grid (token, groups of heads)),
+// the head's elements in the lanes' registers between the turn and the scaling, the sum of squares by shuffles: no
+// barrier, no shared memory, and the same arithmetic for a head whatever the step's size.  Value heads are copied.
+// Head sizes up to 512, rotary sizes up to 512.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+rope_unit_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits, size_t in_split_stride,
+                      TO* __restrict__ q_out, int q_stride, const int* __restrict__ positions,
+                      const int* __restrict__ slots, const float* __restrict__ inv_freq,
+                      TO* __restrict__ k_pages, TO* __restrict__ v_pages, int nq, int nkv, int hd,
+                      int rot_dim, int page_size, int interleaved, int vd, float norm_eps) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x, lane = threadIdx.x & 31;
+    const int h_first = blockIdx.y * 4 + (threadIdx.x >> 5), h_step = 4 * gridDim.y;
+    if (h_first >= nq + 2 * nkv) return;
+    const int slot = slots ? slots[t] : -1;
+    const float pos = (float)positions[t];
+    const int half = rot_dim >> 1;
+    float sn[8], cs[8];          // a lane's pairs are the same in every head: their angles are worked out once
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        sn[u] = 0.f; cs[u] = 1.f;
+        const int j = lane + 32 * u;
+        if (j < half && h_first < nq + nkv) sincosf(pos * inv_freq[j], &sn[u], &cs[u]);
+    }
+    pdl_wait();
+    for (int h = h_first; h < nq + 2 * nkv; h += h_step) {
+        const bool value = h >= nq + nkv;
+        if (h >= nq && slot < 0) return;
+        const TI* x = qkv + (size_t)t * row_stride + (value ? (size_t)(nq + nkv) * hd + (size_t)(h - nq - nkv) * vd : (size_t)h * hd);
+        TO* dst;
+        if (h < nq) dst = q_out + (size_t)t * q_stride + (size_t)h * hd;
+        else {
+            const int kvh = value ? h - nq - nkv : h - nq;
+            dst = (value ? v_pages : k_pages) + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * (value ? vd : hd);
+        }
+        auto in = [&](int c) {
+            float v = to_f32(x[c]);
+            for (int sp = 1; sp < in_splits; ++sp) v += to_f32(x[(size_t)sp * in_split_stride + c]);
+            return v;
+        };
+        if (value) {
+            for (int c = lane; c < vd; c += 32) dst[c] = from_f32<TO>(in(c));
+            continue;
+        }
+        float ya[8], yb[8], yr[16];
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = lane + 32 * u;
+            ya[u] = yb[u] = 0.f;
+            if (j < half) {
+                const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+                rotate_pair(in(ia), in(ib), sn[u], cs[u], ya[u], yb[u]);
+                ss += ya[u] * ya[u] + yb[u] * yb[u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int c = rot_dim + lane + 32 * u;
+            yr[u] = 0.f;
+            if (c < hd) { yr[u] = in(c); ss += yr[u] * yr[u]; }
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = lane + 32 * u;
+            if (j < half) {
+                const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+                dst[ia] = from_f32<TO>(ya[u] * inv);
+                dst[ib] = from_f32<TO>(yb[u] * inv);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const int c = rot_dim + lane + 32 * u;
+            if (c < hd) dst[c] = from_f32<TO>(yr[u] * inv);
+        }
     }
 }
 
@@ -179,16 +237,28 @@ WLLM_API int wllm_rope_kv_write_general(const void* qkv, int in_dtype, int row_s
         return wllm_launch(rope_kv_write_rows_kernel, n, 128, (size_t)rot_dim * sizeof(float), stream, (const bf16*)qkv, row_stride,
                            (bf16*)q_out, q_stride, positions, slots, inv_freq, (bf16*)k_pages, (bf16*)v_pages, nq, nkv, hd,
                            rot_dim, page_size);
+    if (unit_norm) {
+        if (hd > 512) return WLLM_BAD_SIZE;
+        // few tokens: four heads a CTA, so that a token's heads run on different SMs; many: a CTA a token, a warp every fourth head
+        const dim3 ugrid(n, n >= 512 ? 1 : (nq + 2 * nkv + 3) / 4);
+#define UN(TI, TO) wllm_launch(rope_unit_norm_kernel<TI, TO>, ugrid, 128, 0, stream, (const TI*)qkv, row_stride, in_splits, \
+        (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
+        rot_dim, page_size, interleaved, vd, norm_eps)
+        if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) return UN(bf16, bf16);
+        if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) return UN(float, bf16);
+        if (in_dtype == WLLM_F32 && out_dtype == WLLM_F32) return UN(float, float);
+#undef UN
+        return WLLM_BAD_DTYPE;
+    }
     const int threads = hd >= 256 ? 128 : (hd >= 128 ? 64 : 32);
     // One CTA a token once the tokens alone fill the SMs several times over; below that a CTA a head, which keeps a
     // token's heads (and the partial sums each has to add) on different SMs: 256 tokens x 10 heads of 4 parts took
     // 24 us a layer as 256 CTAs and take 6 as 2,560.
     const bool all_heads = n >= 1024;
     const dim3 grid(n, all_heads ? 1 : nq + 2 * nkv);
-    const size_t smem = unit_norm ? (size_t)(hd + 32) * sizeof(float) : 0;
-#define GO2(TI, TO, A) wllm_launch(rope_kv_write_kernel<TI, TO, A>, grid, threads, smem, stream, (const TI*)qkv, row_stride, in_splits, \
+#define GO2(TI, TO, A) wllm_launch(rope_kv_write_kernel<TI, TO, A>, grid, threads, 0, stream, (const TI*)qkv, row_stride, in_splits, \
         (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
-        rot_dim, page_size, interleaved, vd, unit_norm ? 1 : 0, norm_eps)
+        rot_dim, page_size, interleaved, vd)
 #define GO(TI, TO) (all_heads ? GO2(TI, TO, true) : GO2(TI, TO, false))
     if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) return GO(bf16, bf16);
     if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) return GO(float, bf16);
