@@ -49,8 +49,22 @@ ONCE = {   # a loop that runs its layers once, a left mixer without rotation, on
     "loop": {"start": 0, "stop": 2, "times": 1},
 }
 
-CONFIGS = {"mix": MIX, "plain": PLAIN, "once": ONCE}
-SEEDS = {"mix": 5, "plain": 9, "once": 13}
+ODD = {    # sizes that are multiples of little: a width and a feed-forward that are no multiples of 8, key sizes that are no
+           # multiples of 4 or 16, three query heads on one key/value head, a loop over the first layer alone
+    "architecture": "Pesanex", "vocab": 77, "width": 100, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "gla", "mlp": {"kind": "dense", "ff": 50}, "mixer": {"heads": 3, "dim": 18, "vdim": 12, "tau": 5.0, "rank": 3}},
+        {"type": "retention", "mlp": None,
+         "mixer": {"heads": 2, "dim": 20, "vdim": 36, "decay": [0.75, 0.98], "rot": {"dims": 10, "base": 77.0}}},
+        {"type": "parallel", "mlp": {"kind": "dense", "ff": 36},
+         "mixer": {"left": {"heads": 3, "kv_heads": 1, "dim": 24, "vdim": 8, "scale": 0.3, "rot": {"dims": 12, "base": 1000.0}},
+                   "right": {"heads": 1, "dim": 70, "vdim": 66, "tau": 2.5, "rank": 7}}},
+    ],
+    "loop": {"start": 0, "stop": 1, "times": 2},
+}
+
+CONFIGS = {"mix": MIX, "plain": PLAIN, "once": ONCE, "odd": ODD}
+SEEDS = {"mix": 5, "plain": 9, "once": 13, "odd": 17}
 
 
 def write_folder(folder: str, name: str, dtype=torch.bfloat16) -> str:

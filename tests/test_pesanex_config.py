@@ -68,6 +68,17 @@ def test_the_plan_lists_the_checkpoint_tensors_of_every_layer_once():
     assert len(names) == len(model.param_specs())
 
 
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_every_test_configuration_builds_and_gets_seeded_weights(name, tmp_path):
+    folder = write_folder(str(tmp_path / name), name)
+    arch, cfg = config_from_folder(folder)
+    model = ComposedModel(arch.make_plan(cfg), torch.bfloat16)
+    from safetensors.torch import load_file
+    held = load_file(os.path.join(folder, "model.safetensors"))
+    assert set(held) == {ps.name for ps in model.param_specs()}
+    assert len(model.plan.runs) == len(cfg.order()) and len(model.state_specs) >= 1
+
+
 def test_a_rank_that_the_configuration_leaves_out_is_an_open_size():
     raw = copy.deepcopy(PLAIN)
     del raw["layers"][2]["mixer"]["rank"]

@@ -190,7 +190,8 @@ __device__ __forceinline__ void la_cp4(float* smem_dst, const float* src) {
 // registers.  A token's q, k and decay are the same for all lanes: they are read from shared memory four channels at
 // a time, and with two columns a lane every such read feeds eight multiply-adds; one column a lane and one channel
 // a read left the kernel waiting for shared memory (a read a multiply-add).
-template <bool PER_CHANNEL, int MODE>
+// FULL: every warp holds LA_CPT channels (the head's key size is a multiple of 16): the loops carry no guards.
+template <bool PER_CHANNEL, int MODE, bool FULL>
 __global__ void __launch_bounds__(512)
 linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                     const float* __restrict__ decay, const float* __restrict__ head_decay, float* __restrict__ state,
@@ -225,7 +226,7 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
     const float* St = (MODE == 2 && nseg > 1) ? seg_state + (((size_t)(r * max_seg + seg) * H + h) * D) * V : Sg;
 #pragma unroll
     for (int i = 0; i < LA_CPT; ++i) {
-        const bool ch = MODE != 1 && c_lo + i < c_hi;
+        const bool ch = MODE != 1 && (FULL || c_lo + i < c_hi);
         S0[i] = (ch && col0) ? St[(size_t)(c_lo + i) * V + j0] : 0.f;
         S1[i] = (ch && col1) ? St[(size_t)(c_lo + i) * V + j1] : 0.f;
         P[i] = 1.f;
@@ -274,7 +275,7 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
                 const float v0 = qs[NA * Dp + lane], v1 = qs[NA * Dp + 32 + lane];
 #pragma unroll
                 for (int i4 = 0; i4 < LA_CPT; i4 += 4) {
-                    if (c_lo + i4 < c_hi) {
+                    if (FULL || c_lo + i4 < c_hi) {
                         const float4 q4 = *reinterpret_cast<const float4*>(qs + c_lo + i4);
                         const float4 k4 = *reinterpret_cast<const float4*>(qs + Dp + c_lo + i4);
                         float4 a4 = make_float4(fixed, fixed, fixed, fixed);
@@ -282,7 +283,7 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
                         const float qe[4] = {q4.x, q4.y, q4.z, q4.w}, ke[4] = {k4.x, k4.y, k4.z, k4.w}, ae[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            if (c_lo + i4 + e < c_hi) {           // (the last channels of a head whose size is no multiple of 4)
+                            if (FULL || c_lo + i4 + e < c_hi) {   // (the last channels of a head whose size is no multiple of 4)
                                 S0[i4 + e] = fmaf(ae[e], S0[i4 + e], ke[e] * v0);
                                 S1[i4 + e] = fmaf(ae[e], S1[i4 + e], ke[e] * v1);
                                 if (MODE == 1) P[i4 + e] *= ae[e];
@@ -327,7 +328,7 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
         float* Ad = seg_decay + ((size_t)(r * max_seg + seg + 1) * H + h) * D;
 #pragma unroll
         for (int i = 0; i < LA_CPT; ++i)
-            if (c_lo + i < c_hi) {
+            if (FULL || c_lo + i < c_hi) {
                 if (col0) Ld[(size_t)(c_lo + i) * V + j0] = S0[i];
                 if (col1) Ld[(size_t)(c_lo + i) * V + j1] = S1[i];
                 if (blockIdx.x == 0 && lane == 0) Ad[c_lo + i] = P[i];
@@ -337,7 +338,7 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
     if (MODE == 0 || seg == nseg - 1) {
 #pragma unroll
         for (int i = 0; i < LA_CPT; ++i)
-            if (c_lo + i < c_hi) {
+            if (FULL || c_lo + i < c_hi) {
                 if (col0) Sg[(size_t)(c_lo + i) * V + j0] = S0[i];
                 if (col1) Sg[(size_t)(c_lo + i) * V + j1] = S1[i];
             }
@@ -383,18 +384,20 @@ WLLM_API int wllm_linattn_scan(const float* q, const float* k, const float* v, c
     const int warps = (D + cpt - 1) / cpt;
     const int vtiles = (V + LA_COLS - 1) / LA_COLS;
     const size_t smem = ((size_t)2 * LA_TT * ((decay ? 3 : 2) * ((D + 3) & ~3) + LA_COLS) + 2 * warps * LA_TT * 64) * sizeof(float);
+    const bool full = cpt == LA_CPT && D % LA_CPT == 0;
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaSuccess;
-#define RAISE(K) if (e == cudaSuccess) e = cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)
-        RAISE((linattn_scan_kernel<true, 0>)); RAISE((linattn_scan_kernel<true, 1>)); RAISE((linattn_scan_kernel<true, 2>));
-        RAISE((linattn_scan_kernel<false, 0>)); RAISE((linattn_scan_kernel<false, 1>)); RAISE((linattn_scan_kernel<false, 2>));
+#define RAISE(PC, M) if (e == cudaSuccess) e = cudaFuncSetAttribute(linattn_scan_kernel<PC, M, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linattn_scan_kernel<PC, M, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
+        RAISE(true, 0); RAISE(true, 1); RAISE(true, 2); RAISE(false, 0); RAISE(false, 1); RAISE(false, 2);
 #undef RAISE
         if (e != cudaSuccess) return 1000 + (int)e;
         raised = true;
     }
-#define SCAN(PC, MODE, GRID) wllm_launch(linattn_scan_kernel<PC, MODE>, GRID, warps * 32, smem, stream, q, k, v, decay, head_decay, \
+#define SCAN2(PC, MODE, F, GRID) wllm_launch(linattn_scan_kernel<PC, MODE, F>, GRID, warps * 32, smem, stream, q, k, v, decay, head_decay, \
         state, out, req_q_start, req_q_len, req_slot, H, D, V, cpt, seg_len, max_seg, seg_state, seg_decay)
+#define SCAN(PC, MODE, GRID) (full ? SCAN2(PC, MODE, true, GRID) : SCAN2(PC, MODE, false, GRID))
     if (!cut) {
         const dim3 grid(vtiles, H, requests);
         return decay ? SCAN(true, 0, grid) : SCAN(false, 0, grid);
@@ -407,6 +410,7 @@ WLLM_API int wllm_linattn_scan(const float* q, const float* k, const float* v, c
     if (st != WLLM_OK) return st;
     return decay ? SCAN(true, 2, grid) : SCAN(false, 2, grid);
 #undef SCAN
+#undef SCAN2
 }
 
 // ---------------------------------------------------------------------------------------------------

@@ -41,8 +41,6 @@ class PagedAttention:
         self.nq, self.nkv, self.hd = int(spec.num_heads), int(spec.num_kv_heads), int(spec.head_dim)
         if self.nq % self.nkv:
             raise ValueError(f"{self.nq} query heads are no multiple of {self.nkv} key/value heads")
-        if self.hd % 16:
-            raise ValueError(f"head_dim {self.hd}: the attention kernels take head sizes in steps of 16")
         self.window = spec.options.get("window")
         self.hidden_size, self.model_dtype = hidden_size, model_dtype
         self.names = {k: spec.options[k] for k in ("q_proj", "k_proj", "v_proj", "o_proj")}
