@@ -348,7 +348,7 @@ def test_attention_with_sinks_on_the_tensor_core_kernels(T, hd):
 
 
 @pytest.mark.parametrize("per_channel", [True, False])
-@pytest.mark.parametrize("H,D,V", [(2, 24, 40), (3, 16, 8), (1, 130, 33), (4, 64, 64)])
+@pytest.mark.parametrize("H,D,V", [(2, 24, 40), (3, 16, 8), (1, 130, 33), (4, 64, 64), (2, 32, 33), (2, 48, 100), (1, 256, 68)])
 def test_the_recurrence_with_its_state_carried_from_call_to_call(per_channel, H, D, V):
     from wllm_b200.kernels import ops
     g = torch.Generator().manual_seed(H * D + V)

@@ -176,6 +176,10 @@ __device__ __forceinline__ void la_cp4(float* smem_dst, const float* src) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void la_cp16(float* smem_dst, const float* src) {      // both 16-byte aligned
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 
 // MODE 0  a request's tokens of the step in one walk: from its state slot, outputs written, back to the slot.
 // Long portions are cut into segments of `seg_len` tokens that are walked at the same time (grid z = request * max_seg + segment):
@@ -233,9 +237,33 @@ linattn_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, co
     }
     const float fixed = PER_CHANNEL ? 0.f : head_decay[h];
 
+    // rows of whole 16-byte pieces (key sizes in steps of 16, value sizes in steps of 4, aligned buffers): a warp a token,
+    // a lane a piece of q, k and the decay, sixteen lanes a piece of v; no division, a quarter of the copies
+    const bool pieces = FULL && (V & 3) == 0 &&
+        ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (PER_CHANNEL ? (uintptr_t)decay : 0)) & 15) == 0);
     auto load_tile = [&](int tile, int stage) {
         float* dst = stage0 + (size_t)stage * LA_TT * per_token;
         const int first = t0 + tile * LA_TT, count = min(LA_TT, q_len - tile * LA_TT);
+        if (pieces) {
+            for (int tt = warp; tt < count; tt += warps) {
+                const size_t at = ((size_t)(first + tt) * H + h) * D;
+                float* d = dst + tt * per_token;
+                for (int c = 4 * lane; c < D; c += 128) {
+                    la_cp16(d + c, q + at + c);
+                    la_cp16(d + Dp + c, k + at + c);
+                    if (PER_CHANNEL) la_cp16(d + 2 * Dp + c, decay + at + c);
+                }
+                if (lane < LA_COLS / 4) {
+                    const int cc = blockIdx.x * LA_COLS + 4 * lane;
+                    const float* vrow = v + ((size_t)(first + tt) * H + h) * V;
+                    if (cc + 3 < V) la_cp16(d + NA * Dp + 4 * lane, vrow + cc);
+                    else
+                        for (int e = 0; e < 4; ++e) la_cp4(d + NA * Dp + 4 * lane + e, vrow + min(cc + e, V - 1));
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            return;
+        }
         for (int idx = threadIdx.x; idx < count * D; idx += blockDim.x) {
             const int tt = idx / D, c = idx - tt * D;
             const size_t at = ((size_t)(first + tt) * H + h) * D + c;
