@@ -243,6 +243,40 @@ def test_rotation_with_unit_norm_heads_and_value_heads_of_their_own_size(in_part
     assert (got_k.double() - k).abs().max() < 2e-5 and (got_v.double() - v).abs().max() < 1e-6
 
 
+@pytest.mark.parametrize("hd,vd,rot", [(64, 64, 32), (256, 256, 128), (128, 48, 128), (24, 8, 16), (80, 16, 0)])
+def test_rotation_with_unit_norm_heads_over_a_prompt_in_bfloat16(hd, vd, rot):
+    """Prompts in bfloat16 take a kernel of their own (16-byte loads, a warp every fourth head); it agrees with the plain
+    statement, and a portion of few tokens (the head-a-warp kernel) gives the same rows up to the last bit's rounding."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(hd + vd)
+    n, nq, nkv, ps, eps = 300, 5, 2, 16, 1e-6
+    width = (nq + nkv) * hd + nkv * vd
+    fused = torch.randn(n, width + 8, generator=g).bfloat16()
+    positions = torch.arange(7, 7 + n)
+    inv_freq = torch.tensor([300.0 ** (-2.0 * i / max(rot, 1)) for i in range(rot // 2)])
+    pages = -(-n // ps)
+    slots = torch.arange(n, dtype=torch.int32)
+    outs = []
+    for rows in (slice(0, n), slice(0, 40)):
+        m = rows.stop
+        k_pages = torch.zeros(pages, nkv, ps, hd, dtype=torch.bfloat16, device=DEV)
+        v_pages = torch.zeros(pages, nkv, ps, vd, dtype=torch.bfloat16, device=DEV)
+        q_out = torch.empty(m, nq * hd, dtype=torch.bfloat16, device=DEV)
+        ops.rope_kv_write(fused.to(DEV)[:m, :width], q_out, positions[:m].int().to(DEV), slots[:m].to(DEV), inv_freq.to(DEV), k_pages,
+                          v_pages, nq, nkv, hd, rot, ps, vd=vd, unit_norm_eps=eps)
+        outs.append((q_out.cpu().float(), k_pages.cpu().float(), v_pages.cpu().float()))
+    t64 = fused.double()
+    q = plain.unit_rms(plain.rotate_half(t64[:, :nq * hd].view(n, nq, hd), positions, rot, 300.0), eps)
+    k = plain.unit_rms(plain.rotate_half(t64[:, nq * hd:(nq + nkv) * hd].view(n, nkv, hd), positions, rot, 300.0), eps)
+    v = t64[:, (nq + nkv) * hd:width].view(n, nkv, vd)
+    got_q, got_k, got_v = outs[0]
+    assert (got_q.double().view(n, nq, hd) - q).abs().max() < 0.03
+    pk = got_k.view(pages, nkv, ps, hd).permute(0, 2, 1, 3).reshape(pages * ps, nkv, hd)[:n]
+    pv = got_v.view(pages, nkv, ps, vd).permute(0, 2, 1, 3).reshape(pages * ps, nkv, vd)[:n]
+    assert (pk.double() - k).abs().max() < 0.03 and torch.equal(pv.double(), v)
+    assert (outs[1][0] - got_q[:40]).abs().max() < 0.02          # the two kernels round a head's sum in another order
+
+
 def sink_attention_plain(q, k, v, sinks, scale, rep):
     """q [Tq, nq, hd] are the last Tq positions of k, v [T, nkv, .]; float64."""
     T, Tq = k.shape[0], q.shape[0]

@@ -163,6 +163,86 @@ rope_unit_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits,
     }
 }
 
+// The same for prompts in bfloat16 (one input tensor, head sizes, half the rotary size and what lies behind it in steps of 8,
+// aligned rows): a CTA a token; the token's sines and cosines go to shared memory once; a warp takes every fourth head, a
+// lane eight neighbouring pairs (or eight of the elements behind them) with 16-byte loads and stores; value heads are
+// copied sixteen bytes at a time.  Head sizes up to 512.
+__global__ void __launch_bounds__(128)
+rope_unit_norm_rows_kernel(const bf16* __restrict__ qkv, int row_stride, bf16* __restrict__ q_out, int q_stride,
+                           const int* __restrict__ positions, const int* __restrict__ slots, const float* __restrict__ inv_freq,
+                           bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int nq, int nkv, int hd, int rot_dim,
+                           int page_size, int vd, float norm_eps) {
+    extern __shared__ float sc[];            // [half] sines, [half] cosines
+    pdl_launch_dependents();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = slots ? slots[t] : -1;
+    const float pos = (float)positions[t];
+    const int half = rot_dim >> 1;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sc[j], &sc[half + j]);
+    __syncthreads();
+    pdl_wait();
+    const bf16* row = qkv + (size_t)t * row_stride;
+    const int rotated = slot < 0 ? nq : nq + nkv;
+    const int pair_items = half / 8, rest_items = (hd - rot_dim) / 8;       // at most 32 and 64
+    for (int h = warp; h < rotated; h += 4) {
+        const bf16* x = row + (size_t)h * hd;
+        bf16* dst = h < nq ? q_out + (size_t)t * q_stride + (size_t)h * hd
+                           : k_pages + (((size_t)(slot / page_size) * nkv + (h - nq)) * page_size + slot % page_size) * hd;
+        float ya[8], yb[8], yr[2][8];
+        float ss = 0.f;
+        if (lane < pair_items) {
+            const int j = lane * 8;
+            const uint4 a = *reinterpret_cast<const uint4*>(x + j), b = *reinterpret_cast<const uint4*>(x + j + half);
+            const bf16* xa = reinterpret_cast<const bf16*>(&a);
+            const bf16* xb = reinterpret_cast<const bf16*>(&b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                rotate_pair(to_f32(xa[e]), to_f32(xb[e]), sc[j + e], sc[half + j + e], ya[e], yb[e]);
+                ss += ya[e] * ya[e] + yb[e] * yb[e];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int item = lane + 32 * u;
+            if (item < rest_items) {
+                const uint4 r = *reinterpret_cast<const uint4*>(x + rot_dim + item * 8);
+                const bf16* xr = reinterpret_cast<const bf16*>(&r);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { yr[u][e] = to_f32(xr[e]); ss += yr[u][e] * yr[u][e]; }
+            }
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)hd + norm_eps);
+        if (lane < pair_items) {
+            uint4 oa, ob;
+            bf16* pa = reinterpret_cast<bf16*>(&oa);
+            bf16* pb = reinterpret_cast<bf16*>(&ob);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { pa[e] = from_f32<bf16>(ya[e] * inv); pb[e] = from_f32<bf16>(yb[e] * inv); }
+            *reinterpret_cast<uint4*>(dst + lane * 8) = oa;
+            *reinterpret_cast<uint4*>(dst + lane * 8 + half) = ob;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int item = lane + 32 * u;
+            if (item < rest_items) {
+                uint4 o;
+                bf16* po = reinterpret_cast<bf16*>(&o);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) po[e] = from_f32<bf16>(yr[u][e] * inv);
+                *reinterpret_cast<uint4*>(dst + rot_dim + item * 8) = o;
+            }
+        }
+    }
+    if (slot < 0) return;
+    const int whole = vd / 8;
+    for (int item = threadIdx.x; item < nkv * whole; item += blockDim.x) {
+        const int kvh = item / whole, c = (item % whole) * 8;
+        bf16* dst = v_pages + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * vd;
+        *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(row + (size_t)(nq + nkv) * hd + (size_t)kvh * vd + c);
+    }
+}
+
 // Many tokens, bfloat16 in and out, one input tensor, head size and half the rotary size in steps of 8: one
 // CTA a token; the token's sines and cosines go to shared memory once; every thread then takes eight
 // neighbouring pairs of one head with 16-byte loads and stores, so that a block of 128 threads has the heads
@@ -239,6 +319,12 @@ WLLM_API int wllm_rope_kv_write_general(const void* qkv, int in_dtype, int row_s
                            rot_dim, page_size);
     if (unit_norm) {
         if (hd > 512) return WLLM_BAD_SIZE;
+        if (n >= 256 && !interleaved && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && vd % 8 == 0 &&
+            rot_dim % 16 == 0 && row_stride % 8 == 0 && q_stride % 8 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) &&
+            !((uintptr_t)k_pages & 15) && !((uintptr_t)v_pages & 15))
+            return wllm_launch(rope_unit_norm_rows_kernel, n, 128, (size_t)rot_dim * sizeof(float), stream, (const bf16*)qkv, row_stride,
+                               (bf16*)q_out, q_stride, positions, slots, inv_freq, (bf16*)k_pages, (bf16*)v_pages, nq, nkv, hd,
+                               rot_dim, page_size, vd, norm_eps);
         // four heads a CTA at every size.  A CTA a token whose warps walk every fourth head (angles worked out once a lane)
         // was measured slower over a prompt: 2,048 tokens, 10 heads of 256: 76 us against 48
         const dim3 ugrid(n, (nq + 2 * nkv + 3) / 4);
