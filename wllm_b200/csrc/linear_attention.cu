@@ -27,9 +27,19 @@ __device__ __forceinline__ float la_any(const void* p, int dtype, size_t i) {
     return dtype == WLLM_BF16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i]) : reinterpret_cast<const float*>(p)[i];
 }
 // element i of a row that may come as `parts` slabs `stride` elements apart, added in slab order
+// (several parts are always 32-bit slabs; sixteen loads are in flight at a time, only the additions are a chain)
 __device__ __forceinline__ float la_in(const void* p, int dtype, int parts, size_t stride, size_t i) {
-    float v = la_any(p, dtype, i);
-    for (int s = 1; s < parts; ++s) v += la_any(p, dtype, i + (size_t)s * stride);
+    if (parts == 1) return la_any(p, dtype, i);
+    const float* f = reinterpret_cast<const float*>(p) + i;
+    float v = 0.f;
+    for (int s0 = 0; s0 < parts; s0 += 16) {
+        float part[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) part[u] = s0 + u < parts ? f[(size_t)(s0 + u) * stride] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+            if (s0 + u < parts) v = (s0 + u == 0) ? part[u] : v + part[u];
+    }
     return v;
 }
 

@@ -216,9 +216,20 @@ WLLM_API int wllm_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
 __device__ __forceinline__ float any_at(const void* p, int dtype, size_t i) {
     return dtype == WLLM_BF16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i]) : reinterpret_cast<const float*>(p)[i];
 }
+// part 0 + part 1 + ... in that order (several parts are always 32-bit slabs); sixteen loads are in flight at a time,
+// only the additions are a chain
 __device__ __forceinline__ float parts_at(const void* p, int dtype, int parts, size_t stride, size_t i) {
-    float v = any_at(p, dtype, i);
-    for (int s = 1; s < parts; ++s) v += any_at(p, dtype, i + (size_t)s * stride);
+    if (parts == 1) return any_at(p, dtype, i);
+    const float* f = reinterpret_cast<const float*>(p) + i;
+    float v = 0.f;
+    for (int s0 = 0; s0 < parts; s0 += 16) {
+        float part[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) part[u] = s0 + u < parts ? f[(size_t)(s0 + u) * stride] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+            if (s0 + u < parts) v = (s0 + u == 0) ? part[u] : v + part[u];
+    }
     return v;
 }
 // (mean, 1 / sqrt(var + eps)) of one row of a branch
@@ -286,28 +297,31 @@ __global__ void sandwich_norm_kernel(float* __restrict__ resid, const void* __re
                                      const void* __restrict__ wp, int center_p, float eps_p, const void* __restrict__ w,
                                      float offset, int center, float eps, int w_dtype, TO* __restrict__ out,
                                      const int* __restrict__ rows, int H) {
-    extern __shared__ float row_s[];
+    extern __shared__ float row_s[];          // [H] the row between the passes; with two branches [H] more for the second
     __shared__ float scratch[32];
     pdl_begin();
     const int i = blockIdx.x;
     const size_t row0 = (size_t)(rows ? rows[i] : i) * H;
+    float* row_b = row_s + H;
     float inv_a = 1.f, inv_b = 1.f;
+    // the branches' parts are added once and kept: every later pass reads shared memory
+    float ssa = 0.f, ssb = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float x = parts_at(a, a_dtype, a_parts, a_stride, row0 + c);
+        row_s[c] = x;
+        ssa += x * x;
+        if (b) { const float y = parts_at(b, b_dtype, b_parts, b_stride, row0 + c); row_b[c] = y; ssb += y * y; }
+    }
     if (wa) {
-        float ssa = 0.f, ssb = 0.f;
-        for (int c = threadIdx.x; c < H; c += blockDim.x) {
-            const float x = parts_at(a, a_dtype, a_parts, a_stride, row0 + c);
-            ssa += x * x;
-            if (b) { const float y = parts_at(b, b_dtype, b_parts, b_stride, row0 + c); ssb += y * y; }
-        }
         inv_a = 1.0f / sqrtf(block_sum(ssa, scratch) / (float)H + inner_eps);
         if (b) inv_b = 1.0f / sqrtf(block_sum(ssb, scratch) / (float)H + inner_eps);
     }
     float sum = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float u = parts_at(a, a_dtype, a_parts, a_stride, row0 + c);
+        float u = row_s[c];
         if (wa) {
             u = (u * inv_a) * any_at(wa, w_dtype, c);
-            if (b) u += (parts_at(b, b_dtype, b_parts, b_stride, row0 + c) * inv_b) * any_at(wb, w_dtype, c);
+            if (b) u += (row_b[c] * inv_b) * any_at(wb, w_dtype, c);
             u *= factor;
         }
         row_s[c] = u;
@@ -341,11 +355,11 @@ WLLM_API int wllm_sandwich_norm(float* resid, const void* a, int a_dtype, int a_
                                 float eps, int w_dtype, void* out, int out_dtype, const int* rows, int n, int H,
                                 cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
-    if (H <= 0 || H > 48 * 1024 || a_parts < 1 || (b && b_parts < 1) || (b && !wa)) return WLLM_BAD_SIZE;
+    if (H <= 0 || H > 24 * 1024 || a_parts < 1 || (b && b_parts < 1) || (b && !wa)) return WLLM_BAD_SIZE;
     if ((a_dtype != WLLM_BF16 && a_dtype != WLLM_F32) || (w_dtype != WLLM_BF16 && w_dtype != WLLM_F32) ||
         (b && b_dtype != WLLM_BF16 && b_dtype != WLLM_F32))
         return WLLM_BAD_DTYPE;
-    const size_t smem = (size_t)H * sizeof(float);
+    const size_t smem = (size_t)(b ? 2 : 1) * H * sizeof(float);
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(sandwich_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);

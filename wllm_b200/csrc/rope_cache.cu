@@ -117,9 +117,17 @@ rope_unit_norm_kernel(const TI* __restrict__ qkv, int row_stride, int in_splits,
             const int kvh = value ? h - nq - nkv : h - nq;
             dst = (value ? v_pages : k_pages) + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * (value ? vd : hd);
         }
-        auto in = [&](int c) {
-            float v = to_f32(x[c]);
-            for (int sp = 1; sp < in_splits; ++sp) v += to_f32(x[(size_t)sp * in_split_stride + c]);
+        auto in = [&](int c) {     // part 0 + part 1 + ... in order; sixteen loads are in flight at a time
+            if (in_splits == 1) return to_f32(x[c]);
+            float v = 0.f;
+            for (int sp = 0; sp < in_splits; sp += 16) {
+                float part[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) part[u] = sp + u < in_splits ? to_f32(x[(size_t)(sp + u) * in_split_stride + c]) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    if (sp + u < in_splits) v = (sp + u == 0) ? part[u] : v + part[u];
+            }
             return v;
         };
         if (value) {

@@ -65,7 +65,7 @@ class RMSNorm:
 
     def _fusable(self, pending: NormedBranch) -> bool:
         post = pending.norm
-        if not isinstance(post, RMSNorm) or post.offset or post.weight.dtype != self.weight.dtype or self.hidden_size > 48 * 1024:
+        if not isinstance(post, RMSNorm) or post.offset or post.weight.dtype != self.weight.dtype or self.hidden_size > 24 * 1024:
             return False
         inner = pending.branch
         return not isinstance(inner, MeanOfNormed) or inner.gain_a.dtype == self.weight.dtype == inner.gain_b.dtype
