@@ -28,8 +28,10 @@ __device__ __forceinline__ float la_any(const void* p, int dtype, size_t i) {
 }
 // element i of a row that may come as `parts` slabs `stride` elements apart, added in slab order
 // (several parts are always 32-bit slabs; sixteen loads are in flight at a time, only the additions are a chain)
+// MULTI false: the kernel was launched for a single tensor and carries none of the code for parts.
+template <bool MULTI>
 __device__ __forceinline__ float la_in(const void* p, int dtype, int parts, size_t stride, size_t i) {
-    if (parts == 1) return la_any(p, dtype, i);
+    if (!MULTI || parts == 1) return la_any(p, dtype, i);
     const float* f = reinterpret_cast<const float*>(p) + i;
     float v = 0.f;
     for (int s0 = 0; s0 < parts; s0 += 16) {
@@ -50,7 +52,7 @@ constexpr int PREP_RK = 32;      // columns of the low-rank map taken at a time
 
 // TT tokens a CTA: the head's slab of the low-rank matrix is read once for all of them (prompts: 8); a step of few
 // tokens takes one token a CTA, so that tokens x heads CTAs share the work.
-template <int TT>
+template <int TT, bool MULTI>
 __global__ void __launch_bounds__(128)
 linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_stride, int parts, size_t part_stride,
                        int q_off, int k_off, int v_off, int a_off, int n, int H, int D, int V, int rank,
@@ -74,20 +76,20 @@ linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_str
             const size_t row = (size_t)t * row_stride + off;
             float sn, cs, y1, y2;
             sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
-            rotate_pair(la_in(fused, in_dtype, parts, part_stride, row + j),
-                        la_in(fused, in_dtype, parts, part_stride, row + j + half), sn, cs, y1, y2);
+            rotate_pair(la_in<MULTI>(fused, in_dtype, parts, part_stride, row + j),
+                        la_in<MULTI>(fused, in_dtype, parts, part_stride, row + j + half), sn, cs, y1, y2);
             float* dst = base + ((size_t)t * H + h) * D;
             dst[j] = y1 * scale;
             dst[j + half] = y2 * scale;
         }
         for (int idx = threadIdx.x; idx < count * rest; idx += blockDim.x) {
             const int tt = idx / rest, c = rot_dim + idx - tt * rest, t = t_lo + tt;
-            base[((size_t)t * H + h) * D + c] = la_in(fused, in_dtype, parts, part_stride, (size_t)t * row_stride + off + c) * scale;
+            base[((size_t)t * H + h) * D + c] = la_in<MULTI>(fused, in_dtype, parts, part_stride, (size_t)t * row_stride + off + c) * scale;
         }
     }
     for (int idx = threadIdx.x; idx < count * V; idx += blockDim.x) {
         const int tt = idx / V, c = idx - tt * V, t = t_lo + tt;
-        v[((size_t)t * H + h) * V + c] = la_in(fused, in_dtype, parts, part_stride, (size_t)t * row_stride + v_off + h * V + c);
+        v[((size_t)t * H + h) * V + c] = la_in<MULTI>(fused, in_dtype, parts, part_stride, (size_t)t * row_stride + v_off + h * V + c);
     }
     if (a_off < 0) return;
     // z[token][channel] = b2[channel] + sum_r low[token][r] * w2[channel][r]: a thread a channel, TT sums each; the
@@ -107,7 +109,7 @@ linattn_prepare_kernel(const void* __restrict__ fused, int in_dtype, int row_str
             for (int idx = threadIdx.x; idx < TT * PREP_RK; idx += blockDim.x) {
                 const int r = idx / TT, tt = idx % TT;
                 low_s[r][tt] = (tt < count && r < rk)
-                    ? la_in(fused, in_dtype, parts, part_stride, (size_t)(t_lo + tt) * row_stride + a_off + r0 + r) : 0.f;
+                    ? la_in<MULTI>(fused, in_dtype, parts, part_stride, (size_t)(t_lo + tt) * row_stride + a_off + r0 + r) : 0.f;
             }
             float wr[PREP_RK];
             if (vec && rk == PREP_RK) {
@@ -167,12 +169,14 @@ WLLM_API int wllm_linattn_prepare(const void* fused, int in_dtype, int row_strid
     if (a_off >= 0 && (rank <= 0 || !(tau > 0.f) || !w2 || !b2 || !decay)) return WLLM_BAD_SIZE;
     if ((in_dtype != WLLM_BF16 && in_dtype != WLLM_F32) || (a_off >= 0 && w_dtype != WLLM_BF16 && w_dtype != WLLM_F32))
         return WLLM_BAD_DTYPE;
-#define PREP(TT) wllm_launch(linattn_prepare_kernel<TT>, dim3((n + TT - 1) / TT, H), 128, 0, stream, fused, \
+#define PREP2(TT, M) wllm_launch(linattn_prepare_kernel<TT, M>, dim3((n + TT - 1) / TT, H), 128, 0, stream, fused, \
         in_dtype, row_stride, parts, (size_t)part_stride, q_off, k_off, v_off, a_off, n, H, D, V, rank, positions, \
         inv_freq, rot_dim, q_scale, k_scale, w2, b2, w_dtype, a_off >= 0 ? 1.0f / tau : 0.f, q, k, v, decay)
+#define PREP(TT) (parts > 1 ? PREP2(TT, true) : PREP2(TT, false))
     if ((long long)n * H >= 2048) return PREP(8);
     return PREP(1);
 #undef PREP
+#undef PREP2
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -454,7 +458,7 @@ WLLM_API int wllm_linattn_scan(const float* q, const float* k, const float* v, c
 // ---------------------------------------------------------------------------------------------------
 // head norm and gate: grid (tokens, heads), one warp
 // ---------------------------------------------------------------------------------------------------
-template <typename TO>
+template <typename TO, bool MULTI>
 __global__ void head_gate_norm_kernel(const float* __restrict__ o, const void* __restrict__ fused, int in_dtype, int row_stride,
                                       int parts, size_t part_stride, int g_off, const void* __restrict__ w, int w_dtype,
                                       float eps, TO* __restrict__ out, int H, int V) {
@@ -467,7 +471,7 @@ __global__ void head_gate_norm_kernel(const float* __restrict__ o, const void* _
     const float inv = 1.0f / sqrtf(ss / (float)V + eps);
     const size_t grow = (size_t)t * row_stride + g_off + (size_t)h * V;
     for (int c = lane; c < V; c += 32) {
-        const float g = la_in(fused, in_dtype, parts, part_stride, grow + c);
+        const float g = la_in<MULTI>(fused, in_dtype, parts, part_stride, grow + c);
         float y = orow[c] * inv;
         if (w) y *= la_any(w, w_dtype, c);
         out[((size_t)t * H + h) * V + c] = from_f32<TO>(y * (g / (1.0f + expf(-g))));
@@ -481,11 +485,10 @@ WLLM_API int wllm_head_gate_norm(const float* o, const void* fused, int in_dtype
     if (n <= 0) return WLLM_OK;
     if (H <= 0 || H > 65535 || V <= 0 || parts < 1) return WLLM_BAD_SIZE;
     if ((in_dtype != WLLM_BF16 && in_dtype != WLLM_F32) || (w && w_dtype != WLLM_BF16 && w_dtype != WLLM_F32)) return WLLM_BAD_DTYPE;
-    if (out_dtype == WLLM_BF16)
-        return wllm_launch(head_gate_norm_kernel<bf16>, dim3(n, H), 32, 0, stream, o, fused, in_dtype, row_stride, parts,
-                           (size_t)part_stride, g_off, w, w_dtype, eps, (bf16*)out, H, V);
-    if (out_dtype == WLLM_F32)
-        return wllm_launch(head_gate_norm_kernel<float>, dim3(n, H), 32, 0, stream, o, fused, in_dtype, row_stride, parts,
-                           (size_t)part_stride, g_off, w, w_dtype, eps, (float*)out, H, V);
+#define GATE(TO, M) wllm_launch(head_gate_norm_kernel<TO, M>, dim3(n, H), 32, 0, stream, o, fused, in_dtype, row_stride, parts, \
+        (size_t)part_stride, g_off, w, w_dtype, eps, (TO*)out, H, V)
+    if (out_dtype == WLLM_BF16) return parts > 1 ? GATE(bf16, true) : GATE(bf16, false);
+    if (out_dtype == WLLM_F32) return parts > 1 ? GATE(float, true) : GATE(float, false);
+#undef GATE
     return WLLM_BAD_DTYPE;
 }

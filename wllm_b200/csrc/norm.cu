@@ -184,6 +184,7 @@ static int launch_out(float* resid, const void* delta, int delta_splits, size_t 
     if (out_dtype == WLLM_F32) return PICK(float);
 #undef PICK
 #undef GO
+#undef GO2
     return WLLM_BAD_DTYPE;
 }
 
@@ -218,8 +219,11 @@ __device__ __forceinline__ float any_at(const void* p, int dtype, size_t i) {
 }
 // part 0 + part 1 + ... in that order (several parts are always 32-bit slabs); sixteen loads are in flight at a time,
 // only the additions are a chain
+// MULTI false: the kernel was launched for single tensors and carries none of the code for parts (the registers of
+// sixteen loads in flight cost the many-row launches their occupancy: a prompt's branch norm took 49 us with them, 37 without)
+template <bool MULTI>
 __device__ __forceinline__ float parts_at(const void* p, int dtype, int parts, size_t stride, size_t i) {
-    if (parts == 1) return any_at(p, dtype, i);
+    if (!MULTI || parts == 1) return any_at(p, dtype, i);
     const float* f = reinterpret_cast<const float*>(p) + i;
     float v = 0.f;
     for (int s0 = 0; s0 < parts; s0 += 16) {
@@ -233,23 +237,25 @@ __device__ __forceinline__ float parts_at(const void* p, int dtype, int parts, s
     return v;
 }
 // (mean, 1 / sqrt(var + eps)) of one row of a branch
+template <bool MULTI>
 __device__ __forceinline__ void branch_stats(const void* p, int dtype, int parts, size_t stride, size_t row0, int H, int center,
                                              float eps, float* scratch, float& mean, float& inv) {
     mean = 0.f;
     if (center) {
         float sum = 0.f;
-        for (int c = threadIdx.x; c < H; c += blockDim.x) sum += parts_at(p, dtype, parts, stride, row0 + c);
+        for (int c = threadIdx.x; c < H; c += blockDim.x) sum += parts_at<MULTI>(p, dtype, parts, stride, row0 + c);
         mean = block_sum(sum, scratch) / (float)H;
     }
     float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const float v = parts_at(p, dtype, parts, stride, row0 + c) - mean;
+        const float v = parts_at<MULTI>(p, dtype, parts, stride, row0 + c) - mean;
         ss += v * v;
     }
     ss = block_sum(ss, scratch);
     inv = 1.0f / sqrtf(ss / (float)H + eps);
 }
 
+template <bool MULTI>
 __global__ void branch_norm_kernel(const void* __restrict__ a, int a_dtype, int a_parts, size_t a_stride, const void* __restrict__ wa,
                                    const void* __restrict__ b, int b_dtype, int b_parts, size_t b_stride, const void* __restrict__ wb,
                                    int w_dtype, float eps, int center, float factor, float* __restrict__ out, int H) {
@@ -257,11 +263,11 @@ __global__ void branch_norm_kernel(const void* __restrict__ a, int a_dtype, int 
     pdl_begin();
     const size_t row0 = (size_t)blockIdx.x * H;
     float mean_a, inv_a, mean_b = 0.f, inv_b = 0.f;
-    branch_stats(a, a_dtype, a_parts, a_stride, row0, H, center, eps, scratch, mean_a, inv_a);
-    if (b) branch_stats(b, b_dtype, b_parts, b_stride, row0, H, center, eps, scratch, mean_b, inv_b);
+    branch_stats<MULTI>(a, a_dtype, a_parts, a_stride, row0, H, center, eps, scratch, mean_a, inv_a);
+    if (b) branch_stats<MULTI>(b, b_dtype, b_parts, b_stride, row0, H, center, eps, scratch, mean_b, inv_b);
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float y = ((parts_at(a, a_dtype, a_parts, a_stride, row0 + c) - mean_a) * inv_a) * any_at(wa, w_dtype, c);
-        if (b) y += ((parts_at(b, b_dtype, b_parts, b_stride, row0 + c) - mean_b) * inv_b) * any_at(wb, w_dtype, c);
+        float y = ((parts_at<MULTI>(a, a_dtype, a_parts, a_stride, row0 + c) - mean_a) * inv_a) * any_at(wa, w_dtype, c);
+        if (b) y += ((parts_at<MULTI>(b, b_dtype, b_parts, b_stride, row0 + c) - mean_b) * inv_b) * any_at(wb, w_dtype, c);
         out[row0 + c] = y * factor;
     }
 }
@@ -277,7 +283,10 @@ WLLM_API int wllm_branch_norm(const void* a, int a_dtype, int a_parts, long long
         (b && b_dtype != WLLM_BF16 && b_dtype != WLLM_F32))
         return WLLM_BAD_DTYPE;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    return wllm_launch(branch_norm_kernel, n, threads, 0, stream, a, a_dtype, a_parts, (size_t)a_stride, wa, b, b_dtype,
+    if (a_parts > 1 || (b && b_parts > 1))
+        return wllm_launch(branch_norm_kernel<true>, n, threads, 0, stream, a, a_dtype, a_parts, (size_t)a_stride, wa, b, b_dtype,
+                           b_parts, (size_t)b_stride, wb, w_dtype, eps, center ? 1 : 0, factor, out, H);
+    return wllm_launch(branch_norm_kernel<false>, n, threads, 0, stream, a, a_dtype, a_parts, (size_t)a_stride, wa, b, b_dtype,
                        b_parts, (size_t)b_stride, wb, w_dtype, eps, center ? 1 : 0, factor, out, H);
 }
 
@@ -290,7 +299,7 @@ WLLM_API int wllm_branch_norm(const void* a, int a_dtype, int a_parts, long long
 // The row lives in shared memory between the passes (H floats); every sum is a block sum in a fixed order.
 // With `rows` the residual is read at rows[i] and left as it is (the last norm at the places whose logits are wanted).
 // ---------------------------------------------------------------------------------------------------
-template <typename TO>
+template <typename TO, bool MULTI>
 __global__ void sandwich_norm_kernel(float* __restrict__ resid, const void* __restrict__ a, int a_dtype, int a_parts, size_t a_stride,
                                      const void* __restrict__ wa, const void* __restrict__ b, int b_dtype, int b_parts,
                                      size_t b_stride, const void* __restrict__ wb, float inner_eps, float factor,
@@ -307,10 +316,10 @@ __global__ void sandwich_norm_kernel(float* __restrict__ resid, const void* __re
     // the branches' parts are added once and kept: every later pass reads shared memory
     float ssa = 0.f, ssb = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const float x = parts_at(a, a_dtype, a_parts, a_stride, row0 + c);
+        const float x = parts_at<MULTI>(a, a_dtype, a_parts, a_stride, row0 + c);
         row_s[c] = x;
         ssa += x * x;
-        if (b) { const float y = parts_at(b, b_dtype, b_parts, b_stride, row0 + c); row_b[c] = y; ssb += y * y; }
+        if (b) { const float y = parts_at<MULTI>(b, b_dtype, b_parts, b_stride, row0 + c); row_b[c] = y; ssb += y * y; }
     }
     if (wa) {
         inv_a = 1.0f / sqrtf(block_sum(ssa, scratch) / (float)H + inner_eps);
@@ -362,17 +371,23 @@ WLLM_API int wllm_sandwich_norm(float* resid, const void* a, int a_dtype, int a_
     const size_t smem = (size_t)(b ? 2 : 1) * H * sizeof(float);
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(sandwich_norm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(sandwich_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+        cudaError_t e = cudaSuccess;
+#define RAISE(K) if (e == cudaSuccess) e = cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024)
+        RAISE((sandwich_norm_kernel<bf16, true>)); RAISE((sandwich_norm_kernel<bf16, false>));
+        RAISE((sandwich_norm_kernel<float, true>)); RAISE((sandwich_norm_kernel<float, false>));
+#undef RAISE
         if (e != cudaSuccess) return 1000 + (int)e;
         raised = true;
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define GO(TO) wllm_launch(sandwich_norm_kernel<TO>, n, threads, smem, stream, resid, a, a_dtype, a_parts, (size_t)a_stride, wa, b, \
+    const bool multi = a_parts > 1 || (b && b_parts > 1);
+#define GO2(TO, M) wllm_launch(sandwich_norm_kernel<TO, M>, n, threads, smem, stream, resid, a, a_dtype, a_parts, (size_t)a_stride, wa, b, \
         b_dtype, b_parts, (size_t)b_stride, wb, inner_eps, factor, wp, center_p ? 1 : 0, eps_p, w, offset, center ? 1 : 0, eps, \
         w_dtype, (TO*)out, rows, H)
+#define GO(TO) (multi ? GO2(TO, true) : GO2(TO, false))
     if (out_dtype == WLLM_BF16) return GO(bf16);
     if (out_dtype == WLLM_F32) return GO(float);
 #undef GO
+#undef GO2
     return WLLM_BAD_DTYPE;
 }
