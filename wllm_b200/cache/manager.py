@@ -6,7 +6,8 @@ size and how much of the past they read (all of it, or a window).  Every group h
 its own pool of pages and its own table per request; one page of a group holds
 `page_size` tokens of all the group's layers.  Pages are taken when a step reserves
 room for new tokens and given back when the request is closed, or, in a window
-group, as soon as no later token can read them.  Reserving for a step is atomic:
+group, as soon as no later token can read them (the pages of the first `keep_first`
+tokens of a sequence, which such a group may keep readable behind the window, stay).  Reserving for a step is atomic:
 either every request of the step gets its pages or nothing changes and
 `OutOfPages` is raised, which is how the scheduler learns that it has to preempt.
 
@@ -39,6 +40,7 @@ class CacheGroupSpec:
     head_dim: int
     window: int | None = None   # None: every key is kept; n: a token reads the n latest keys (itself included)
     v_head_dim: int | None = None   # size of a value head when it differs from head_dim
+    keep_first: int = 0             # with a window: the first keys of a sequence that stay readable behind it
 
 
 @dataclass(frozen=True)
@@ -223,7 +225,8 @@ class CacheManager:
                 continue
             first_needed = rc.num_tokens - w + 1          # oldest key the next token reads
             upto = min(max(0, first_needed // self.page_size), len(rc.tables[gi]))
-            passed = list(range(rc.released_upto[gi], upto))
+            kept = -(-g.spec.keep_first // self.page_size)       # pages that hold a sequence's kept first keys stay
+            passed = list(range(max(rc.released_upto[gi], kept), upto))
             g.give([rc.tables[gi][i] for i in passed])
             for i in passed:
                 rc.tables[gi][i] = -1

@@ -12,20 +12,29 @@ __device__ __forceinline__ float act_silu(float x) { return x / (1.0f + expf(-x)
 template <int ACT> __device__ __forceinline__ float act_apply(float x) {
     return ACT == 0 ? act_gelu_tanh(x) : ACT == 1 ? act_silu(x) : fmaxf(x, 0.f);
 }
+// the whole gated unit: act(g) * u for the plain activations, the clamped form for ACT 3
+template <int ACT> __device__ __forceinline__ float gated_unit(float g, float u, float limit, float slope) {
+    if (ACT == 3) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return (g / (1.0f + expf(-slope * g))) * (u + 1.0f);
+    }
+    return act_apply<ACT>(g) * u;
+}
 
 template <typename T, int ACT>
-__global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total) {
+__global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total, float limit, float slope) {
     pdl_begin();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t n = idx / I, c = idx % I;
         const float g = to_f32(in[n * 2 * I + c]), u = to_f32(in[n * 2 * I + I + c]);
-        out[idx] = from_f32<T>(act_apply<ACT>(g) * u);
+        out[idx] = from_f32<T>(gated_unit<ACT>(g, u, limit, slope));
     }
 }
 
 // bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores, grid (column blocks, rows)
 template <int ACT>
-__global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int I) {
+__global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int I, float limit, float slope) {
     pdl_begin();
     const int n = blockIdx.y;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
@@ -39,27 +48,46 @@ __global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ in, bf16* __res
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
-        o2[i] = __floats2bfloat162_rn(act_apply<ACT>(g.x) * u.x, act_apply<ACT>(g.y) * u.y);
+        o2[i] = __floats2bfloat162_rn(gated_unit<ACT>(g.x, u.x, limit, slope), gated_unit<ACT>(g.y, u.y, limit, slope));
     }
     *reinterpret_cast<uint4*>(out + (size_t)n * I + c) = ov;
 }
 
-WLLM_API int wllm_gated_act(const void* in, void* out, int dtype, int act, int n, int I, cudaStream_t stream) {
+WLLM_API int wllm_gated_act_params(const void* in, void* out, int dtype, int act, int n, int I, float limit, float slope,
+                                   cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (I <= 0) return WLLM_BAD_SIZE;
-    if (act < 0 || act > 2) return WLLM_BAD_SIZE;
+    if (act < 0 || act > 3) return WLLM_BAD_SIZE;
     if (dtype == WLLM_BF16 && I % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         const dim3 grid((I / 8 + 127) / 128, n);
-        if (act == 0) return wllm_launch(gated_act_bf16x8_kernel<0>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I);
-        if (act == 2) return wllm_launch(gated_act_bf16x8_kernel<2>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I);
-        return wllm_launch(gated_act_bf16x8_kernel<1>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I);
+#define LAUNCH8(A) wllm_launch(gated_act_bf16x8_kernel<A>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I, limit, slope)
+        return act == 0 ? LAUNCH8(0) : act == 1 ? LAUNCH8(1) : act == 2 ? LAUNCH8(2) : LAUNCH8(3);
+#undef LAUNCH8
     }
     const size_t total = (size_t)n * I;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-#define LAUNCH(T, A) wllm_launch(gated_act_kernel<T, A>, blocks, threads, 0, stream, (const T*)in, (T*)out, I, total)
-    if (dtype == WLLM_BF16) return act == 0 ? LAUNCH(bf16, 0) : act == 1 ? LAUNCH(bf16, 1) : LAUNCH(bf16, 2);
-    if (dtype == WLLM_F32) return act == 0 ? LAUNCH(float, 0) : act == 1 ? LAUNCH(float, 1) : LAUNCH(float, 2);
+#define LAUNCH(T, A) wllm_launch(gated_act_kernel<T, A>, blocks, threads, 0, stream, (const T*)in, (T*)out, I, total, limit, slope)
+    if (dtype == WLLM_BF16) return act == 0 ? LAUNCH(bf16, 0) : act == 1 ? LAUNCH(bf16, 1) : act == 2 ? LAUNCH(bf16, 2) : LAUNCH(bf16, 3);
+    if (dtype == WLLM_F32) return act == 0 ? LAUNCH(float, 0) : act == 1 ? LAUNCH(float, 1) : act == 2 ? LAUNCH(float, 2) : LAUNCH(float, 3);
 #undef LAUNCH
     return WLLM_BAD_DTYPE;
+}
+
+WLLM_API int wllm_gated_act(const void* in, void* out, int dtype, int act, int n, int I, cudaStream_t stream) {
+    if (act == 3) return WLLM_BAD_SIZE;      // the clamped unit has constants: wllm_gated_act_params
+    return wllm_gated_act_params(in, out, dtype, act, n, I, 0.f, 0.f, stream);
+}
+
+__global__ void tanh_cap_kernel(float* __restrict__ x, size_t total, float cap) {
+    pdl_begin();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] = cap * tanhf(x[idx] / cap);
+}
+
+WLLM_API int wllm_tanh_cap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return WLLM_OK;
+    if (!(cap > 0.f)) return WLLM_BAD_SIZE;
+    const long long want = (total + 255) / 256;
+    return wllm_launch(tanh_cap_kernel, (int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream, x, (size_t)total, cap);
 }

@@ -31,9 +31,18 @@
 // value, neither scaled nor counted twice.  It enters when a row is finished, after the last chunk was merged:
 //   m' = max(m, s_h);  l' = l e^(m-m') + e^(s_h-m');  out = o e^(m-m') / l'
 //
+// Two more options of the score rule and the mask.  `cap` > 0: a score becomes cap * tanh(score / cap) after the
+// scale.  `keep` > 0 (with a window): the first `keep` keys of a sequence stay visible behind the window, at their
+// true positions: key j is seen from position p when j <= p and (p - j < window or j < keep).  A row then touches
+// the chunks of its kept keys (from chunk 0 on) and the chunks of its window, each once, in ascending order; tiles
+// of 32 keys without a visible key are passed by (their pages may have been given back).
+//
 // Used for the 32-bit path at every size, and for bfloat16 at the sizes that the
 // tensor-core kernels refuse.
 #include "common.cuh"
+
+constexpr int WARPS = 4;
+constexpr int CHUNK = 64;
 
 template <typename T> struct Vec;
 template <> struct Vec<float> {
@@ -56,23 +65,41 @@ template <> struct Vec<bf16> {
     }
 };
 
-constexpr int WARPS = 4;
-constexpr int CHUNK = 64;
+
+// What a row at position `pos` sees: the keys [0, kept) and [first, pos] (kept = 0: no keys behind the window, or the
+// two runs touch and first = 0).  Its chunks: 0 .. head_chunks-1, then first_chunk .. last_chunk.
+struct RowKeys { int first, kept, first_chunk, last_chunk, head_chunks; };
+__device__ __forceinline__ RowKeys row_keys(int pos, int window, int keep) {
+    RowKeys r;
+    r.first = window > 0 ? max(0, pos - window + 1) : 0;
+    r.kept = 0;
+    if (keep > 0) {
+        if (r.first <= keep) r.first = 0; else r.kept = keep;
+    }
+    r.first_chunk = r.first / CHUNK;
+    r.last_chunk = pos / CHUNK;
+    r.head_chunks = r.kept > 0 ? min((r.kept - 1) / CHUNK + 1, r.first_chunk) : 0;
+    return r;
+}
+__device__ __forceinline__ int row_chunk(const RowKeys& r, int slot) { return slot < r.head_chunks ? slot : r.first_chunk + slot - r.head_chunks; }
+__device__ __forceinline__ int row_chunk_count(const RowKeys& r) { return r.head_chunks + r.last_chunk - r.first_chunk + 1; }
 
 // The partial result of one chunk of one row (every lane holds m and l; lane x holds o of the dimensions e*32+x).
 template <typename T, int NE>
 __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, const T* __restrict__ k_pages,
                                               const T* __restrict__ v_pages, const int* __restrict__ table, int nkv,
-                                              int kvh, int hd, int vd, int page_size, int first, int pos, int chunk, float scale,
-                                              int lane, float& m, float& l, float (&o)[NE]) {
+                                              int kvh, int hd, int vd, int page_size, int first, int kept, int pos, int chunk, float scale,
+                                              float cap, int lane, float& m, float& l, float (&o)[NE]) {
     m = -INFINITY;
     l = 0.f;
 #pragma unroll
     for (int e = 0; e < NE; ++e) o[e] = 0.f;
-    const int lo = max(chunk * CHUNK, (first >> 5) << 5), hi = min(chunk * CHUNK + CHUNK - 1, pos);
+    const int lo = chunk * CHUNK < kept ? chunk * CHUNK : max(chunk * CHUNK, (first >> 5) << 5), hi = min(chunk * CHUNK + CHUNK - 1, pos);
     for (int tile = lo; tile <= hi; tile += 32) {
         const int key = tile + lane;
-        const bool valid = key >= first && key <= pos;
+        const bool valid = (key >= first || key < kept) && key <= pos;
+        const unsigned seen = __ballot_sync(0xffffffffu, valid);
+        if (seen == 0u) continue;             // a tile between the kept keys and the window
         float s = -INFINITY;
         int row = -1;  // index of the key's row of head_dim elements inside the pool
         if (valid) {
@@ -88,6 +115,7 @@ __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, cons
                 for (int i = 0; i < Vec<T>::N; ++i) acc[i & 3] = fmaf(qs[d + i], kv[i], acc[i & 3]);
             }
             s = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * scale;
+            if (cap > 0.f) s = cap * tanhf(s / cap);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -98,7 +126,7 @@ __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, cons
         // values of eight keys are requested before the first of them is used; a key outside the row's range
         // (only at its two ends) adds fma(0, v, o) = o with the values of a key inside it
         const int count = min(32, pos - tile + 1);
-        const int safe = __shfl_sync(0xffffffffu, row, min(31, pos - tile));     // the row's last key of this tile: always valid
+        const int safe = __shfl_sync(0xffffffffu, row, 31 - __clz(seen));     // the row's last visible key of this tile
         constexpr int VA = NE <= 8 ? 8 : 4;      // value rows asked for together
         for (int j0 = 0; j0 < count; j0 += VA) {
             float pj[VA], vj[VA][NE];
@@ -172,7 +200,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
                             const int* __restrict__ token_req, const int* __restrict__ positions,
                             const int* __restrict__ block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
                             int page_size, int window, float scale, float* __restrict__ scratch, int max_chunks,
-                            int vd, const float* __restrict__ sinks) {
+                            int vd, const float* __restrict__ sinks, float cap, int keep) {
     extern __shared__ float q_smem[];
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -181,12 +209,11 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     const int token = item / nq, head = item % nq;
     const int kvh = head / (nq / nkv);
     const int pos = positions[token];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    const int first_chunk = first / CHUNK, last_chunk = pos / CHUNK;
-    int c0 = first_chunk, c1 = last_chunk;
+    const RowKeys rk = row_keys(pos, window, keep);
+    int c0 = 0, c1 = row_chunk_count(rk) - 1;           // slots of the row's list of chunks
     if (SPLIT) {
-        c0 = first_chunk + (int)blockIdx.y;
-        if (c0 > last_chunk) return;
+        c0 = (int)blockIdx.y;
+        if (c0 > c1) return;
         if ((int)blockIdx.y < max_chunks - 1) c1 = c0;
     }
     const int* table = block_table + (size_t)token_req[token] * max_pages;
@@ -198,9 +225,10 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     float m = -INFINITY, l = 0.f, o[NE];
 #pragma unroll
     for (int e = 0; e < NE; ++e) o[e] = 0.f;
-    for (int chunk = c0; chunk <= c1; ++chunk) {
+    for (int slot = c0; slot <= c1; ++slot) {
         float mc, lc, oc[NE];
-        chunk_partial<T, NE>(qs, k_pages, v_pages, table, nkv, kvh, hd, vd, page_size, first, pos, chunk, scale, lane, mc, lc, oc);
+        chunk_partial<T, NE>(qs, k_pages, v_pages, table, nkv, kvh, hd, vd, page_size, rk.first, rk.kept, pos, row_chunk(rk, slot),
+                             scale, cap, lane, mc, lc, oc);
         merge_chunk<NE>(m, l, o, mc, lc, oc);
     }
     if (SPLIT) {
@@ -220,15 +248,14 @@ template <typename T, int NE>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_attention_simt_merge_kernel(T* __restrict__ out, int out_stride, const int* __restrict__ positions, int n_tokens,
                                   int nq, int hd, int window, const float* __restrict__ scratch, int max_chunks,
-                                  const float* __restrict__ sinks) {
+                                  const float* __restrict__ sinks, int keep) {
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * WARPS + warp;
     if (item >= n_tokens * nq) return;
     const int token = item / nq, head = item % nq;
     const int pos = positions[token];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    const int slots = min(max_chunks, pos / CHUNK - first / CHUNK + 1);
+    const int slots = min(max_chunks, row_chunk_count(row_keys(pos, window, keep)));
     float m = -INFINITY, l = 0.f, o[NE];
 #pragma unroll
     for (int e = 0; e < NE; ++e) o[e] = 0.f;
@@ -260,7 +287,7 @@ template <typename T>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                   const int* token_req, const int* positions, const int* block_table, int max_pages, int n_tokens,
                   int nq, int nkv, int hd, int page_size, int window, float scale, float* scratch, int max_chunks,
-                  int vd, const float* sinks, cudaStream_t stream) {
+                  int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
     const int blocks = (n_tokens * nq + WARPS - 1) / WARPS;
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
     const bool split = scratch != nullptr && max_chunks > 1;
@@ -268,13 +295,13 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
         if (!split) \
             return wllm_launch(paged_attention_simt_kernel<T, NE, false>, blocks, WARPS * 32, smem, stream, \
                 (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, positions, \
-                block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks); \
+                block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep); \
         const int st = wllm_launch(paged_attention_simt_kernel<T, NE, true>, dim3(blocks, max_chunks), WARPS * 32, smem, \
                 stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, \
-                positions, block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks); \
+                positions, block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep); \
         if (st != WLLM_OK) return st; \
         return wllm_launch(paged_attention_simt_merge_kernel<T, NE>, blocks, WARPS * 32, 0, stream, (T*)out, out_stride, \
-                positions, n_tokens, nq, vd, window, (const float*)scratch, max_chunks, sinks); \
+                positions, n_tokens, nq, vd, window, (const float*)scratch, max_chunks, sinks, keep); \
     } while (0)
     if (vd <= 64) GO(2);
     if (vd <= 128) GO(4);
@@ -291,8 +318,9 @@ WLLM_API int wllm_paged_attention_simt_general(const void* q, int q_stride, void
                                                const void* v_pages, int dtype, const int* token_req, const int* positions,
                                                const int* block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
                                                int page_size, int window, float scale, float* scratch, int max_chunks,
-                                               int vd, const float* sinks, cudaStream_t stream) {
+                                               int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
     if (n_tokens <= 0) return WLLM_OK;
+    if (keep < 0 || cap < 0.f || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
     // key rows are read with 16-byte loads: head sizes come in steps of 8 up to 512
     if (hd <= 0 || hd > 512 || hd % 8 != 0 || vd <= 0 || vd > 512 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 ||
         max_pages <= 0)
@@ -301,11 +329,11 @@ WLLM_API int wllm_paged_attention_simt_general(const void* q, int q_stride, void
     if (dtype == WLLM_BF16) {
         if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
         return launch<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
-                            n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, stream);
+                            n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, stream);
     }
     if (dtype == WLLM_F32)
         return launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
-                             n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, stream);
+                             n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, vd, sinks, cap, keep, stream);
     return WLLM_BAD_DTYPE;
 }
 
@@ -317,7 +345,7 @@ WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, i
     if (hd % 16 != 0) return WLLM_BAD_SIZE;
     return wllm_paged_attention_simt_general(q, q_stride, out, out_stride, k_pages, v_pages, dtype, token_req, positions,
                                              block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale, scratch,
-                                             max_chunks, hd, nullptr, stream);
+                                             max_chunks, hd, nullptr, 0.f, 0, stream);
 }
 
 // --------------------------------------------------------------------------------------
@@ -338,7 +366,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
                                   const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
                                   const int* __restrict__ req_ctx_len, const int* __restrict__ block_table, int max_pages,
                                   int nq, int nkv, int hd, int page_size, int window, float scale, int vd,
-                                  const float* __restrict__ sinks) {
+                                  const float* __restrict__ sinks, float cap, int keep) {
     constexpr int VN = Vec<T>::N;                  // elements of a 16-byte piece
     extern __shared__ __align__(16) unsigned char tl_smem[];
     pdl_begin();
@@ -355,12 +383,14 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
     const int* table = block_table + (size_t)r * max_pages;
 
     // this warp's rows: position, first key, where they are stored
-    int pos_r[TL_RPW], first_r[TL_RPW];
+    int pos_r[TL_RPW], first_r[TL_RPW], kept_r[TL_RPW];
 #pragma unroll
     for (int i = 0; i < TL_RPW; ++i) {
         const int m = m0 + warp * TL_RPW + i;
         pos_r[i] = m < rows ? pos0 + m / rep : -1;                          // a row past the end takes no key
-        first_r[i] = window > 0 ? max(0, pos_r[i] - window + 1) : 0;
+        const RowKeys rk = row_keys(max(pos_r[i], 0), window, keep);
+        first_r[i] = rk.first;
+        kept_r[i] = rk.kept;
     }
     for (int idx = threadIdx.x; idx < TL_ROWS * hd; idx += blockDim.x) {
         const int m = m0 + idx / hd, d = idx % hd;
@@ -369,14 +399,19 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
     // the keys that the CTA's rows see, in tiles of 32 at absolute multiples of 32
     const int last_m = min(rows, m0 + TL_ROWS) - 1;
     const int key_hi = pos0 + last_m / rep + 1;                              // one past the last row's position
-    const int key_lo = window > 0 ? max(0, pos0 + m0 / rep - window + 1) : 0;
+    const RowKeys top = row_keys(pos0 + m0 / rep, window, keep);             // the CTA's first row reaches furthest back
+    const int key_lo = top.first, kept = top.kept;
     const int t_lo = key_lo >> 5, t_hi = (key_hi + 31) >> 5;
+    // the tiles of the kept keys that lie before the window's first tile come first; then the window's tiles
+    const int head_tiles = kept > 0 ? min((kept + 31) >> 5, t_lo) : 0;
+    const int n_tiles = head_tiles + max(t_hi - t_lo, 0);
+    auto tile_at = [&](int idx) { return idx < head_tiles ? idx : t_lo + idx - head_tiles; };
 
     auto load_tile = [&](int t, int stage) {
         const int kp = hd / VN, pieces = kp + vd / VN;      // 16-byte pieces of a key's row and of its value's
         for (int c = threadIdx.x; c < 32 * pieces; c += blockDim.x) {
             const int kl = c / pieces, piece = c % pieces, key = t * 32 + kl;
-            const bool valid = key >= key_lo && key < key_hi;           // others are zero: their weight is zero, their values must be numbers
+            const bool valid = (key >= key_lo || key < kept) && key < key_hi;           // others are zero: their weight is zero, their values must be numbers
             size_t row = 0;
             if (valid) row = ((size_t)table[key / page_size] * nkv + g) * page_size + key % page_size;
             if (piece < kp) cp_async_16(ks + ((size_t)stage * 32 + kl) * kld + piece * VN, k_pages + row * hd + piece * VN, valid);
@@ -394,10 +429,10 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
 #pragma unroll
         for (int e = 0; e < NE; ++e) o_t[i][e] = o_c[i][e] = 0.f;
     }
-    if (t_lo < t_hi) load_tile(t_lo, 0);
-    for (int t = t_lo; t < t_hi; ++t) {
-        const int stage = (t - t_lo) & 1;
-        if (t + 1 < t_hi) load_tile(t + 1, stage ^ 1); else asm volatile("cp.async.commit_group;" ::: "memory");
+    if (n_tiles > 0) load_tile(tile_at(0), 0);
+    for (int idx = 0; idx < n_tiles; ++idx) {
+        const int t = tile_at(idx), stage = idx & 1;
+        if (idx + 1 < n_tiles) load_tile(tile_at(idx + 1), stage ^ 1); else asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();                          // tile t is here for everyone (and the queries, the first time)
         const T* kt = ks + (size_t)stage * 32 * kld;
@@ -407,7 +442,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
         bool act[TL_RPW], any = false;
 #pragma unroll
         for (int i = 0; i < TL_RPW; ++i) {
-            act[i] = !(tile > pos_r[i] || tile + 31 < first_r[i]);
+            act[i] = tile <= pos_r[i] && (tile + 31 >= first_r[i] || tile < kept_r[i]);
             any = any || act[i];
         }
         if (any) {
@@ -439,8 +474,9 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
             for (int i = 0; i < TL_RPW; ++i) {
                 p[i] = 0.f;
                 if (!act[i]) continue;
-                const bool valid = key >= first_r[i] && key <= pos_r[i];
-                const float s = valid ? ((acc[i][0] + acc[i][1]) + (acc[i][2] + acc[i][3])) * scale : -INFINITY;
+                const bool valid = (key >= first_r[i] || key < kept_r[i]) && key <= pos_r[i];
+                float s = valid ? ((acc[i][0] + acc[i][1]) + (acc[i][2] + acc[i][3])) * scale : -INFINITY;
+                if (valid && cap > 0.f) s = cap * tanhf(s / cap);
                 const float m_new = fmaxf(m_c[i], warp_max(s));
                 p[i] = valid ? expf(s - m_new) : 0.f;
                 const float corr = expf(m_c[i] - m_new);
@@ -469,7 +505,7 @@ paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __re
             }
         }
         // the end of a chunk of 64 keys (or of the row): its result joins the row's
-        const bool chunk_ends = ((t + 1) & (CHUNK / 32 - 1)) == 0 || t + 1 == t_hi;
+        const bool chunk_ends = ((t + 1) & (CHUNK / 32 - 1)) == 0 || idx + 1 == n_tiles || tile_at(idx + 1) != t + 1;
 #pragma unroll
         for (int i = 0; i < TL_RPW; ++i) {
             if (open_c[i] && (chunk_ends || tile + 32 > pos_r[i])) {
@@ -494,7 +530,7 @@ template <typename T>
 static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                         const int* req_q_start, const int* req_q_len, const int* req_ctx_len, const int* block_table,
                         int max_pages, int requests, int max_q_len, int nq, int nkv, int hd, int page_size, int window,
-                        float scale, int vd, const float* sinks, cudaStream_t stream) {
+                        float scale, int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
     const int rep = nq / nkv;
     const dim3 grid((max_q_len * rep + TL_ROWS - 1) / TL_ROWS, nkv, requests);
     const size_t smem = (size_t)TL_ROWS * hd * sizeof(float) + 2 * 32 * ((size_t)(hd + Vec<T>::N) + vd) * sizeof(T);
@@ -508,7 +544,7 @@ static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, 
         } \
         return wllm_launch(paged_attention_simt_tiled_kernel<T, NE>, grid, TL_WARPS * 32, smem, stream, (const T*)q, q_stride, \
                            (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, req_q_start, req_q_len, req_ctx_len, \
-                           block_table, max_pages, nq, nkv, hd, page_size, window, scale, vd, sinks); \
+                           block_table, max_pages, nq, nkv, hd, page_size, window, scale, vd, sinks, cap, keep); \
     } while (0)
     const int smem_max = TL_ROWS * 256 * (int)sizeof(float) + 2 * 32 * ((256 + Vec<T>::N) + 256) * (int)sizeof(T);
     if (vd <= 64) GO(2);
@@ -523,8 +559,9 @@ WLLM_API int wllm_paged_attention_simt_tiled_general(const void* q, int q_stride
                                                      const void* v_pages, int dtype, const int* req_q_start, const int* req_q_len,
                                                      const int* req_ctx_len, const int* block_table, int max_pages, int requests,
                                                      int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
-                                                     int vd, const float* sinks, cudaStream_t stream) {
+                                                     int vd, const float* sinks, float cap, int keep, cudaStream_t stream) {
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
+    if (keep < 0 || cap < 0.f || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
     if (hd <= 0 || hd > 256 || hd % 8 != 0 || vd <= 0 || vd > 256 || vd % 8 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_pages <= 0 ||
         nkv > 65535 || requests > 65535)
         return WLLM_BAD_SIZE;
@@ -532,12 +569,12 @@ WLLM_API int wllm_paged_attention_simt_tiled_general(const void* q, int q_stride
         if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
         return launch_tiled<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
                                   block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, vd, sinks,
-                                  stream);
+                                  cap, keep, stream);
     }
     if (dtype == WLLM_F32)
         return launch_tiled<float>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
                                    block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, vd, sinks,
-                                   stream);
+                                   cap, keep, stream);
     return WLLM_BAD_DTYPE;
 }
 
@@ -549,5 +586,5 @@ WLLM_API int wllm_paged_attention_simt_tiled(const void* q, int q_stride, void* 
     if (hd % 16 != 0) return WLLM_BAD_SIZE;
     return wllm_paged_attention_simt_tiled_general(q, q_stride, out, out_stride, k_pages, v_pages, dtype, req_q_start, req_q_len,
                                                    req_ctx_len, block_table, max_pages, requests, max_q_len, nq, nkv, hd,
-                                                   page_size, window, scale, hd, nullptr, stream);
+                                                   page_size, window, scale, hd, nullptr, 0.f, 0, stream);
 }

@@ -1,5 +1,5 @@
 // Scaled embedding gather: out[n, :] = float(table[ids[n], :]) * scale, written to the
-// 32-bit residual stream.  One block per token, 16-byte loads where the row allows.
+// 32-bit residual stream; with a table of learned position rows, + float(pos_table[positions[n], :]).  One block per token, 16-byte loads where the row allows.
 // And the patch that lets a step start before the host has seen the previous step's tokens:
 // ids[dst[i]] = sampled[src[i]], device to device.
 #include "common.cuh"
@@ -18,7 +18,8 @@ WLLM_API int wllm_patch_tokens(int* ids, const int* dst, const int* sampled, con
 
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table, float scale,
-                                    float* __restrict__ out, int H, int V) {
+                                    float* __restrict__ out, int H, int V, const T* __restrict__ pos_table,
+                                    const int* __restrict__ positions, int P) {
     pdl_begin();
     const int row = blockIdx.x;
     int id = ids[row];
@@ -28,17 +29,33 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __rest
         return;
     }
     const T* src = table + (size_t)id * H;
+    if (pos_table != nullptr) {
+        const int p = positions[row];
+        if (p >= 0 && p < P) {   // the host checks the length of a sequence against the table
+            const T* pr = pos_table + (size_t)p * H;
+            for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = __fadd_rn(__fmul_rn(to_f32(src[c]), scale), to_f32(pr[c]));
+            return;
+        }
+    }
     for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = to_f32(src[c]) * scale;
+}
+
+// pos_table (null: none): [P, H] rows of the table's element type, added at positions[n]
+WLLM_API int wllm_embed_gather_pos(const int* ids, const void* table, int table_dtype, float scale, float* out,
+                                   int n, int H, int V, const void* pos_table, const int* positions, int P, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (H <= 0 || V <= 0 || (pos_table != nullptr && (positions == nullptr || P <= 0))) return WLLM_BAD_SIZE;
+    const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+    if (table_dtype == WLLM_BF16)
+        return wllm_launch(embed_gather_kernel<bf16>, n, threads, 0, stream, ids, (const bf16*)table, scale, out, H, V,
+                           (const bf16*)pos_table, positions, P);
+    if (table_dtype == WLLM_F32)
+        return wllm_launch(embed_gather_kernel<float>, n, threads, 0, stream, ids, (const float*)table, scale, out, H, V,
+                           (const float*)pos_table, positions, P);
+    return WLLM_BAD_DTYPE;
 }
 
 WLLM_API int wllm_embed_gather(const int* ids, const void* table, int table_dtype, float scale, float* out,
                                int n, int H, int V, cudaStream_t stream) {
-    if (n <= 0) return WLLM_OK;
-    if (H <= 0 || V <= 0) return WLLM_BAD_SIZE;
-    const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
-    if (table_dtype == WLLM_BF16)
-        return wllm_launch(embed_gather_kernel<bf16>, n, threads, 0, stream, ids, (const bf16*)table, scale, out, H, V);
-    if (table_dtype == WLLM_F32)
-        return wllm_launch(embed_gather_kernel<float>, n, threads, 0, stream, ids, (const float*)table, scale, out, H, V);
-    return WLLM_BAD_DTYPE;
+    return wllm_embed_gather_pos(ids, table, table_dtype, scale, out, n, H, V, nullptr, nullptr, 0, stream);
 }

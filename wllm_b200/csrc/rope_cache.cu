@@ -8,7 +8,8 @@
 // Dimensions from rot_dim up to head_dim pass through unrotated.  The rotated queries go to `q_out`
 // [n, nq * hd].  The input row may come as `in_splits` partial sums (slabs `in_split_stride` elements
 // apart, as the split-K matrix product leaves them), which are added in slab order first.  A token
-// whose slot is negative writes nothing to the cache (a layer that reads another layer's cache).
+// whose slot is negative writes nothing to the cache (a layer that reads another layer's cache); with nkv = 0 and no
+// slots the row holds query heads alone.
 // Value heads may have a size of their own (`vd`): the fused row is nq heads of hd, nkv heads of hd, nkv heads
 // of vd.  With `unit_norm` every rotated query and key head is divided by its root mean square,
 // y / sqrt(mean(y^2) + norm_eps), in 32-bit, before it is rounded and stored.
@@ -317,7 +318,7 @@ WLLM_API int wllm_rope_kv_write_general(const void* qkv, int in_dtype, int row_s
                                         int rot_dim, int page_size, int interleaved, int vd, int unit_norm, float norm_eps,
                                         cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
-    if (hd <= 0 || vd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv <= 0 || in_splits < 1)
+    if (hd <= 0 || vd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv < 0 || (nkv == 0 && slots != nullptr) || in_splits < 1)
         return WLLM_BAD_SIZE;
     if (n >= 256 && !interleaved && vd == hd && !unit_norm && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && rot_dim % 16 == 0 &&
         row_stride % 8 == 0 && q_stride % 8 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) &&

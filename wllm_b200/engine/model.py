@@ -30,6 +30,14 @@ class ComposedModel:
 
     def _assign_caches(self):
         keys, layers, states, refs = [], [], [], []
+        # a run whose cache other runs read keeps what the widest of their masks sees: the longest window (or every key)
+        # and the most kept first keys
+        readers = {}
+        for run in self.plan.runs:
+            if run.cache_from is not None:
+                need = self.blocks[run.block].cache_need()
+                readers.setdefault(run.cache_from, []).extend(n for n in (need if isinstance(need, (tuple, list)) else (need,))
+                                                              if isinstance(n, KVNeed))
         for i, run in enumerate(self.plan.runs):
             if run.cache_from is not None:
                 src = refs[run.cache_from]
@@ -42,7 +50,13 @@ class ComposedModel:
                     if ref.group is not None:
                         raise TypeError(f"run {i}: a mixer reads the pages of one cache group")
                     vd = one.v_head_dim if one.v_head_dim and one.v_head_dim != one.head_dim else None
-                    key = (one.kv_heads, one.head_dim, one.window, vd)
+                    window, keep = one.window, one.keep_first if one.window is not None else 0
+                    for other in readers.get(i, ()):
+                        if (other.kv_heads, other.head_dim, other.v_head_dim or other.head_dim) != (one.kv_heads, one.head_dim, one.v_head_dim or one.head_dim):
+                            raise TypeError(f"a run that reads the cache of run {i} has other key/value heads than it")
+                        window = None if window is None or other.window is None else max(window, other.window)
+                        keep = max(keep, other.keep_first)
+                    key = (one.kv_heads, one.head_dim, window, vd, keep if window is not None else 0)
                     if key not in keys:
                         keys.append(key)
                         layers.append(0)
@@ -58,9 +72,10 @@ class ComposedModel:
                     raise TypeError(f"run {i}: cache_need() returned {one!r}; expected KVNeed, StateNeed, None or a tuple of them")
             refs.append(ref)
         groups = []
-        for (kvh, hd, window, vd), n in zip(keys, layers):
-            name = ("all" if window is None else f"window{window}") + f"-{kvh}x{hd}" + (f"v{vd}" if vd else "")
-            groups.append(CacheGroupSpec(name, n, kvh, hd, window, vd))
+        for (kvh, hd, window, vd, keep), n in zip(keys, layers):
+            name = ("all" if window is None else f"window{window}") + (f"+first{keep}" if keep else "") + f"-{kvh}x{hd}" + \
+                (f"v{vd}" if vd else "")
+            groups.append(CacheGroupSpec(name, n, kvh, hd, window, vd, keep))
         return groups, states, refs
 
     # -- weights -------------------------------------------------------------------

@@ -88,14 +88,23 @@ def _int32(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
-def embed_gather(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> torch.Tensor:
-    """out[n, :] = float(table[ids[n], :]) * scale; `out` is the float32 residual stream."""
-    _need_cuda(ids, table, out)
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor,
+                 pos_table: torch.Tensor | None = None, positions: torch.Tensor | None = None) -> torch.Tensor:
+    """out[n, :] = float(table[ids[n], :]) * scale (+ float(pos_table[positions[n], :]) with a table of learned
+    position rows); `out` is the float32 residual stream."""
+    _need_cuda(ids, table, out, pos_table, positions)
     n, (V, H) = ids.shape[0], table.shape
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (n, H) and table.is_contiguous()
+    P = 0
+    if pos_table is not None:
+        P = pos_table.shape[0]
+        assert pos_table.shape == (P, H) and pos_table.is_contiguous() and pos_table.dtype == table.dtype
+        assert positions is not None and positions.shape[0] == n
+        positions = _int32(positions, "positions")
     lib = load_family("embedding")
-    _check(lib.wllm_embed_gather(_ptr(_int32(ids, "ids")), _ptr(table), _dt(table), c_float(scale), _ptr(out),
-                                 n, H, V, _stream()), "embed_gather")
+    _check(lib.wllm_embed_gather_pos(_ptr(_int32(ids, "ids")), _ptr(table), _dt(table), c_float(scale), _ptr(out),
+                                     n, H, V, _ptr(pos_table), _ptr(positions if pos_table is not None else None), P,
+                                     _stream()), "embed_gather")
     return out
 
 
@@ -188,6 +197,33 @@ def sandwich_norm(resid: torch.Tensor, a, out: torch.Tensor, post_weight: torch.
                                   _ptr(_int32(rows, "rows") if rows is not None else None), n, H, _stream()), "sandwich_norm")
     return out
 
+def hyper_norm(src: torch.Tensor, dst: torch.Tensor, S: int, branch, prev_mix, prev_out, in_w, gain: torch.Tensor, eps: float,
+               out: torch.Tensor, rows=None) -> torch.Tensor:
+    """A residual of S streams and the norm in front of a sublayer (csrc/hyper_connections.cu).  `src`: the streams
+    [S, n, H] float32, or one [n, H] that every stream is read from; `dst`: where the streams are written [S, n, H] (may be
+    `src`).  `branch`: None, or (tensor [n, H] | float32 partial sums [P, n, H], P or 0), the output of the sublayer before,
+    which joins the streams first: x_t <- sum_s prev_mix[s, t] x_s + prev_out[t] y.  Then out = rmsnorm(sum_s in_w[s] x_s)
+    * gain (in_w None: the plain sum).  With `rows` the streams are read at those rows and left as they are."""
+    _need_cuda(src, dst, gain, out, rows, prev_mix, prev_out, in_w, branch[0] if branch is not None else None)
+    n, H = dst.shape[1], dst.shape[2]
+    assert dst.shape[0] == S and dst.dtype == torch.float32 == src.dtype and dst.is_contiguous() and src.is_contiguous()
+    assert tuple(src.shape) in ((S, n, H), (n, H)) and gain.shape == (H,) and gain.dtype == torch.float32 and gain.is_contiguous()
+    n_out = rows.shape[0] if rows is not None else n
+    assert out.shape == (n_out, H) and out.is_contiguous()
+    for t, shape in ((prev_mix, (S, S)), (prev_out, (S,)), (in_w, (S,))):
+        assert t is None or (t.dtype == torch.float32 and tuple(t.shape) == shape and t.is_contiguous())
+    if branch is not None:
+        assert prev_mix is not None and prev_out is not None
+        pb = _branch_args(branch, n, H)
+    else:
+        pb = (_ptr(None), _F32, 1, ctypes.c_longlong(0))
+    lib = load_family("hyper_connections")
+    _check(lib.wllm_hyper_norm(_ptr(src), ctypes.c_longlong(n * H if src.dim() == 3 else 0), _ptr(dst), ctypes.c_longlong(n * H),
+                               S, *pb, _ptr(prev_mix), _ptr(prev_out), _ptr(in_w), _ptr(gain), c_float(eps), _ptr(out), _dt(out),
+                               _ptr(_int32(rows, "rows") if rows is not None else None), n_out, H, _stream()), "hyper_norm")
+    return out
+
+
 def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor,
                   k_pages, v_pages, nq: int, nkv: int, hd: int, rot_dim: int, page_size: int, in_splits: int = 0,
                   pairing: str = "half", vd: int | None = None, unit_norm_eps: float | None = None) -> None:
@@ -201,7 +237,8 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tenso
         raise KernelError(f"rotary pairing {pairing!r} not supported (half, interleaved)")
     _need_cuda(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages)
     vd = hd if vd is None else vd
-    width = (nq + nkv) * hd + nkv * vd
+    width = (nq + nkv) * hd + nkv * vd          # nkv = 0: a row of query heads alone (nothing goes to the pages)
+    assert nkv > 0 or slots is None
     if in_splits:
         assert qkv.dim() == 3 and qkv.shape[0] == in_splits and qkv.stride(2) == 1 and qkv.dtype == torch.float32
         n, row_stride, split_stride = qkv.shape[1], qkv.stride(1), qkv.stride(0)
@@ -225,21 +262,22 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tenso
 SIMT_CHUNK = 64    # keys per chunk of the one-warp-per-row attention (csrc/attention_simt.cu)
 
 
-def simt_chunks(max_ctx: int, window: int) -> int:
+def simt_chunks(max_ctx: int, window: int, keep: int = 0) -> int:
     """Upper bound of the chunks of 64 keys that a row of a step touches, from the longest context of the
-    step (and the window, if the layer has one)."""
+    step (and the window, if the layer has one, with the first keys it keeps behind it)."""
     most = -(-max(1, max_ctx) // SIMT_CHUNK)
-    return min(most, -(-window // SIMT_CHUNK) + 1) if window > 0 else most
+    return min(most, -(-window // SIMT_CHUNK) + 1 + -(-keep // SIMT_CHUNK)) if window > 0 else most
 
 
 def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                          token_req: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                          nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
                          scratch: torch.Tensor | None = None, max_chunks: int = 0, vd: int | None = None,
-                         sinks: torch.Tensor | None = None) -> torch.Tensor:
+                         sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0) -> torch.Tensor:
     """q: [n, nq*hd] view (row stride free); pages: [num_pages, nkv, page_size, hd]; out: [n, nq*hd].
     `vd`: size of a value head when it is not hd (value pages [.., vd], out [n, nq*vd]); `sinks`: float32 [nq], one
-    more term e^(sink) in every row's softmax denominator.
+    more term e^(sink) in every row's softmax denominator.  `cap` > 0: scores become cap * tanh(score / cap);
+    `keep` > 0 (with a window): the sequence's first `keep` keys stay visible behind the window.
     With `scratch` (float32, n * nq * max_chunks * (hd + 2) floats) and max_chunks = simt_chunks(...) > 1 every
     (row, chunk of 64 keys) gets a warp of its own and a second kernel merges them; the result is the same,
     bit for bit, as without."""
@@ -259,7 +297,7 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
                                                  _ptr(_int32(positions, "positions")), _ptr(_int32(block_table, "block_table")),
                                                  block_table.shape[1], n, nq, nkv, hd, page_size, window, c_float(scale),
                                                  _ptr(scratch), max_chunks if scratch is not None else 0, vd, _ptr(sinks),
-                                                 _stream()), f"paged_attention_simt(head_dim={hd}/{vd}, heads={nq}/{nkv})")
+                                                 c_float(cap), keep, _stream()), f"paged_attention_simt(head_dim={hd}/{vd}, heads={nq}/{nkv})")
     if scratch is not None and max_chunks > 1:
         global launches
         launches += 1    # the merge kernel
@@ -270,7 +308,7 @@ def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torc
                                req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_ctx_len: torch.Tensor,
                                block_table: torch.Tensor, max_q_len: int, nq: int, nkv: int, hd: int, page_size: int,
                                window: int, scale: float, vd: int | None = None,
-                               sinks: torch.Tensor | None = None) -> torch.Tensor:
+                               sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0) -> torch.Tensor:
     """The same attention as `paged_attention_simt`, bit for bit, for steps that bring portions of prompts: a CTA
     takes 32 rows of one (request, key/value head) and reads every tile of keys and values once for all of them
     (csrc/attention_simt.cu, tiled).  Head sizes up to 256; requests are given by their start, length and context."""
@@ -287,7 +325,7 @@ def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torc
                                                        _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                                        _ptr(_int32(block_table, "block_table")), block_table.shape[1],
                                                        req_q_len.shape[0], max_q_len, nq, nkv, hd, page_size, window,
-                                                       c_float(scale), vd, _ptr(sinks), _stream()),
+                                                       c_float(scale), vd, _ptr(sinks), c_float(cap), keep, _stream()),
            f"paged_attention_simt_tiled(head_dim={hd}/{vd}, heads={nq}/{nkv})")
     return out
 
@@ -426,17 +464,31 @@ def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_
            f"attention_mma_prefill(head_dim={hd}, heads={nq}/{nkv})")
 
 
-def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: str) -> torch.Tensor:
-    """out[n, c] = act(gate_up[n, c]) * gate_up[n, I + c]."""
+ACTIVATIONS = {"gelu_tanh": 0, "silu": 1, "relu": 2, "capped_swish": 3}
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: str, limit: float = 0.0, slope: float = 0.0) -> torch.Tensor:
+    """out[n, c] = act(gate_up[n, c]) * gate_up[n, I + c]; 'capped_swish' (with `limit` and `slope`):
+    g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(slope * g) * (u + 1)."""
     _need_cuda(gate_up, out)
     n, two_i = gate_up.shape
     assert gate_up.is_contiguous() and out.is_contiguous() and out.shape == (n, two_i // 2) and out.dtype == gate_up.dtype
-    code = {"gelu_tanh": 0, "silu": 1, "relu": 2}.get(act)
+    code = ACTIVATIONS.get(act)
     if code is None:
-        raise KernelError(f"activation {act!r} not supported (gelu_tanh, silu, relu)")
+        raise KernelError(f"activation {act!r} not supported ({', '.join(ACTIVATIONS)})")
     lib = load_family("activation")
-    _check(lib.wllm_gated_act(_ptr(gate_up), _ptr(out), _dt(gate_up), code, n, two_i // 2, _stream()), "gated_act")
+    _check(lib.wllm_gated_act_params(_ptr(gate_up), _ptr(out), _dt(gate_up), code, n, two_i // 2, c_float(limit),
+                                     c_float(slope), _stream()), "gated_act")
     return out
+
+
+def tanh_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap), in place on a contiguous 32-bit tensor."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous() and cap > 0
+    lib = load_family("activation")
+    _check(lib.wllm_tanh_cap(_ptr(x), ctypes.c_longlong(x.numel()), c_float(cap), _stream()), "tanh_cap")
+    return x
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -655,14 +707,16 @@ def project(a: torch.Tensor, w: torch.Tensor, buffer) -> tuple:
     return linear(a, w, buffer("product", (n, N), a.dtype)), 0
 
 
-def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.Tensor, scratch) -> torch.Tensor:
-    """out[n, I] = act(a @ gate^T) * (a @ up^T) with w_gate_up = [gate; up].  bfloat16 with enough rows: one
+def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.Tensor, scratch, limit: float = 0.0,
+                 slope: float = 0.0) -> torch.Tensor:
+    """out[n, I] = act(a @ gate^T) * (a @ up^T) with w_gate_up = [gate; up] ('capped_swish': the clamped unit of
+    gated_act, with its `limit` and `slope`).  bfloat16 with enough rows: one
     tensor-memory GEMM whose epilogue applies the activation; otherwise product, then activation kernel
     (`scratch(shape, dtype)` supplies the [n, 2I] intermediate)."""
-    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_gate_up):
+    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_gate_up) and act in _TC_EPILOGUES:
         return gemm_bf16_tc(a, w_gate_up, out, act, checked=True)
     gu = linear(a, w_gate_up, scratch((a.shape[0], w_gate_up.shape[0]), a.dtype))
-    return gated_act(gu, out, act)
+    return gated_act(gu, out, act, limit, slope)
 
 
 def _fused_args(fused, parts: int):
@@ -767,6 +821,72 @@ def head_gate_norm(o: torch.Tensor, fused, parts: int, gate_off: int, weight, ep
     _check(lib.wllm_head_gate_norm(_ptr(o), ptr, dt, row_stride, nparts, part_stride, gate_off, _ptr(weight),
                                    _dt(weight) if weight is not None else _F32, c_float(eps), _ptr(out), _dt(out), n, heads,
                                    vdim, _stream()), "head_gate_norm")
+    return out
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, w_gate, chosen: torch.Tensor, weights: torch.Tensor, gate_out,
+              groups: int = 1, groups_kept: int = 1) -> None:
+    """The router of routed experts (csrc/moe.cu): scores = softmax(w_router x) in 32-bit over all E experts, the choice
+    limited to the `groups_kept` best of `groups` groups of neighbouring experts; chosen [n, top] (descending score) and
+    weights [n, top] (the scores as they are).  With `w_gate` [H], gate_out[n] = sigmoid(w_gate . x)."""
+    _need_cuda(x, w_router, w_gate, chosen, weights, gate_out)
+    n, H = x.shape
+    E, top = w_router.shape[0], chosen.shape[1]
+    assert x.is_contiguous() and w_router.dtype == torch.float32 and w_router.shape == (E, H) and w_router.is_contiguous()
+    assert chosen.shape == weights.shape == (n, top) and chosen.dtype == torch.int32 and weights.dtype == torch.float32
+    assert chosen.is_contiguous() and weights.is_contiguous()
+    if w_gate is not None:
+        assert w_gate.dtype == torch.float32 and w_gate.shape == (H,) and w_gate.is_contiguous()
+        assert gate_out.dtype == torch.float32 and gate_out.shape == (n,) and gate_out.is_contiguous()
+    lib = load_family("moe")
+    _check(lib.wllm_moe_route(_ptr(x), _dt(x), _ptr(w_router), _ptr(w_gate), _ptr(chosen), _ptr(weights), _ptr(gate_out), n, H, E,
+                              top, groups, groups_kept, _stream()), f"moe_route(experts={E}, top={top}, groups={groups}/{groups_kept})")
+
+
+def moe_plan(chosen: torch.Tensor, count: torch.Tensor, offset: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+    """The (token, rank) pairs of `chosen` [n, top] sorted by expert, stably: count [E], offset [E + 1], order [pairs] (sorted
+    row -> pair), place [pairs] (pair -> sorted row)."""
+    _need_cuda(chosen, count, offset, order, place)
+    pairs, E = chosen.numel(), count.shape[0]
+    assert offset.shape == (E + 1,) and order.shape == place.shape == (pairs,)
+    for t in (chosen, count, offset, order, place):
+        assert t.dtype == torch.int32 and t.is_contiguous()
+    lib = load_family("moe")
+    _check(lib.wllm_moe_plan(_ptr(chosen), pairs, E, _ptr(count), _ptr(offset), _ptr(order), _ptr(place), _stream()), "moe_plan")
+    global launches
+    launches += 1
+
+
+def moe_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offset: torch.Tensor, order: torch.Tensor, top: int,
+                gated: bool, limit: float = 0.0, slope: float = 0.0) -> torch.Tensor:
+    """The experts' products over rows sorted by expert.  gated: a [n, K] holds the tokens' rows (sorted row r reads row
+    order[r] // top), w [E, 2N, K] = [gate; up] per expert, out [pairs, N] = the clamped gated unit, in the operands' type.
+    Otherwise a [pairs, K] holds sorted rows, w [E, N, K], out [pairs, N] float32.  32-bit accumulation."""
+    _need_cuda(a, w, out, offset, order)
+    E, pairs, K = w.shape[0], order.shape[0], a.shape[1]
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    assert a.dtype == w.dtype and a.stride(1) == 1 and w.is_contiguous() and w.shape[2] == K and out.is_contiguous()
+    assert out.shape == (pairs, N) and out.dtype == (a.dtype if gated else torch.float32) and offset.shape == (E + 1,)
+    assert gated or a.shape[0] == pairs
+    lib = load_family("moe")
+    _check(lib.wllm_moe_grouped(_ptr(a), a.stride(0), _ptr(w), _ptr(out), _dt(a), 1 if gated else 0, pairs, N, K,
+                                _ptr(_int32(offset, "offset")), _ptr(_int32(order, "order")), E, top, c_float(limit), c_float(slope),
+                                _stream()), f"moe_grouped({pairs}x{N}x{K}, {E} experts)")
+    return out
+
+
+def moe_combine(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared, gate, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum over ranks k, in order, of weights[t, k] * y[place[t * top + k]]  (+ gate[t] * shared[t]; `shared`:
+    None or (tensor [n, H] | float32 partial sums [P, n, H], P or 0))."""
+    _need_cuda(y, place, weights, gate, out, shared[0] if shared is not None else None)
+    n, top = weights.shape
+    H = y.shape[1]
+    assert y.dtype == torch.float32 == out.dtype and y.is_contiguous() and out.is_contiguous() and out.shape == (n, H)
+    assert place.shape == (n * top,) and weights.dtype == torch.float32 and weights.is_contiguous()
+    ps = _branch_args(shared, n, H) if shared is not None else (_ptr(None), _F32, 1, ctypes.c_longlong(0))
+    lib = load_family("moe")
+    _check(lib.wllm_moe_combine(_ptr(y), _ptr(_int32(place, "place")), _ptr(weights), top, *ps, _ptr(gate), _ptr(out), n, H,
+                                _stream()), "moe_combine")
     return out
 
 

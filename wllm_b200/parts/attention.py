@@ -12,7 +12,11 @@ head_dim; the output projection then reads num_heads * value_dim columns), scale
 score factor in place of head_dim^-0.5), sink (checkpoint name of one number per query
 head that joins the softmax denominator as e^sink, without key or value),
 qk_unit_norm_eps (rotated q and k heads are divided by their root mean square,
-y / sqrt(mean(y^2) + eps), before the scores).
+y / sqrt(mean(y^2) + eps), before the scores), softcap (c: a score becomes c * tanh(score / c) after the scale),
+keep_first (with a window: the first keys of a sequence stay visible behind it, at their true positions: key j
+is seen from position i when j <= i and (i - j < window or j < keep_first)), reads_other_cache (the mixer has no key
+and value projections, names no k_proj and v_proj, and must stand in a run that reads another run's cache; its queries,
+mask, scale and cap are its own).
 
 A mixer may be one of several that read the same input (a block that runs two mixers side
 by side): `input_weights()` lists the matrices that read the input, `mix(fused, parts,
@@ -43,7 +47,13 @@ class PagedAttention:
             raise ValueError(f"{self.nq} query heads are no multiple of {self.nkv} key/value heads")
         self.window = spec.options.get("window")
         self.hidden_size, self.model_dtype = hidden_size, model_dtype
-        self.names = {k: spec.options[k] for k in ("q_proj", "k_proj", "v_proj", "o_proj")}
+        self.borrows = bool(spec.options.get("reads_other_cache", False))
+        self.names = {k: spec.options[k] for k in (("q_proj", "o_proj") if self.borrows else ("q_proj", "k_proj", "v_proj", "o_proj"))}
+        cap = spec.options.get("softcap")
+        self.softcap = 0.0 if cap is None else float(cap)
+        self.keep_first = int(spec.options.get("keep_first") or 0) if self.window else 0
+        if self.softcap < 0 or self.keep_first < 0:
+            raise ValueError("softcap and keep_first must not be negative")
         self.position = POSITIONS.build(spec.position)
         self.vd = int(spec.options.get("value_dim") or self.hd)
         if self.vd % 8 or self.hd % 8:
@@ -53,25 +63,30 @@ class PagedAttention:
         self.sink_name = spec.options.get("sink")
         self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
         # the tensor-core kernels take keys and values of one size; other shapes run on the general kernels
-        self.general = self.vd != self.hd
-        self.width = (self.nq + self.nkv) * self.hd + self.nkv * self.vd      # columns of the fused q|k|v row
+        self.general = self.vd != self.hd or self.softcap > 0 or self.keep_first > 0
+        # columns of the fused q|k|v row (q alone in a mixer that reads another's keys and values)
+        self.width = self.nq * self.hd if self.borrows else (self.nq + self.nkv) * self.hd + self.nkv * self.vd
         self.tag = ""                    # set by a mixer that runs this one beside another: keeps their buffers apart
         self.wqkv = self.wo = self.sinks = None
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.hd, self.window, self.vd if self.vd != self.hd else None)
+        return KVNeed(self.nkv, self.hd, self.window, self.vd if self.vd != self.hd else None, self.keep_first)
 
     def param_specs(self):
         H, n = self.hidden_size, self.names
-        out = [ParamSpec(n["q_proj"], (self.nq * self.hd, H)), ParamSpec(n["k_proj"], (self.nkv * self.hd, H)),
-               ParamSpec(n["v_proj"], (self.nkv * self.vd, H)), ParamSpec(n["o_proj"], (H, self.nq * self.vd))]
+        out = [ParamSpec(n["q_proj"], (self.nq * self.hd, H)), ParamSpec(n["o_proj"], (H, self.nq * self.vd))]
+        if not self.borrows:
+            out[1:1] = [ParamSpec(n["k_proj"], (self.nkv * self.hd, H)), ParamSpec(n["v_proj"], (self.nkv * self.vd, H))]
         if self.sink_name is not None:
             out.append(ParamSpec(self.sink_name, (self.nq,), "vector"))
         return out
 
     def load(self, fetch):
         n = self.names
-        self.wqkv = torch.cat([fetch(n["q_proj"]), fetch(n["k_proj"]), fetch(n["v_proj"])], dim=0).contiguous()
+        if self.borrows:
+            self.wqkv = fetch(n["q_proj"]).contiguous()
+        else:
+            self.wqkv = torch.cat([fetch(n["q_proj"]), fetch(n["k_proj"]), fetch(n["v_proj"])], dim=0).contiguous()
         self.wo = fetch(n["o_proj"]).contiguous()
         if self.sink_name is not None:
             self.sinks = fetch(self.sink_name).to(torch.float32).contiguous()
@@ -86,6 +101,8 @@ class PagedAttention:
 
     def mix(self, fused: torch.Tensor, parts: int, col0: int, ctx, cache: CacheRef):
         """The mixer on columns col0 .. col0 + width of a fused product [n, W] (or partial sums [parts, n, W])."""
+        if self.borrows == cache.writes:
+            raise ValueError("an attention mixer without key and value projections reads another run's cache, and only such a one")
         n = fused.shape[-2]
         qkv = fused if fused.shape[-1] == self.width else fused[..., col0:col0 + self.width]
         group = ctx.cache.groups[cache.group]
@@ -97,7 +114,7 @@ class PagedAttention:
         if self.unit_norm_eps is not None:
             extra["unit_norm_eps"] = float(self.unit_norm_eps)
         ops.rope_kv_write(qkv, q, ctx.positions, ctx.group_slots[cache.group] if cache.writes else None,
-                          self.position.inv_freq, k_pages, v_pages, self.nq, self.nkv, self.hd,
+                          self.position.inv_freq, k_pages, v_pages, self.nq, 0 if self.borrows else self.nkv, self.hd,
                           self.position.rotary_dim, group.page_size, in_splits=parts,
                           pairing=getattr(self.position, "pairing", "half"), **extra)
         attn = ctx.buffer(self.tag + "attn", (n, self.nq * self.vd), self.model_dtype)
@@ -113,11 +130,13 @@ class PagedAttention:
             # 32 rows of a request share every tile of keys.  Few rows over long contexts (decoding): a warp per
             # (row, chunk of 64 keys).  Otherwise a warp per row.
             extra = {"vd": self.vd, "sinks": self.sinks} if (self.general or self.sinks is not None) else {}
+            if self.softcap > 0 or self.keep_first > 0:
+                extra.update(cap=self.softcap, keep=self.keep_first)
             if ctx.num_multi > 0 and hd <= 256 and self.vd <= 256:
                 ops.paged_attention_simt_tiled(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len,
                                                table, ctx.max_q_len, nq, nkv, hd, ps, window, scale, **extra)
                 return
-            rows, chunks = q.shape[0] * nq, ops.simt_chunks(ctx.max_ctx, window)
+            rows, chunks = q.shape[0] * nq, ops.simt_chunks(ctx.max_ctx, window, self.keep_first)
             scratch = None
             if chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
                 scratch = ctx.buffer(self.tag + "attention_chunks", (rows * chunks * (self.vd + 2),), torch.float32)

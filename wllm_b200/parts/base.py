@@ -76,6 +76,7 @@ class KVNeed:
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None    # size of a value head when it differs from head_dim
+    keep_first: int = 0              # with a window: the sequence's first keys that stay visible behind it
 
 
 @dataclass(frozen=True)

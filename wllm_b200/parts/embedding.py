@@ -5,7 +5,9 @@ scale_in_model_dtype: Gemma multiplies by sqrt(hidden_size) held in the model's
 element type (src/wllm/models/llama.py:397-403, src/wllm/models/gemma.py:158-162),
 so under bfloat16 the factor is the bfloat16 value nearest to the square root; the
 product itself goes to the 32-bit residual unrounded.
-Head spec options: tied (bool), weight (checkpoint name when not tied), vocab_size.
+A further option, position_table (checkpoint name) with max_positions: a learned row per position, added unscaled.
+Head spec options: tied (bool), weight (checkpoint name when not tied), vocab_size, softcap (c: the logits become
+c * tanh(logits / c), in 32-bit; absent or None: as they are).
 The tied head multiplies by the unscaled table (src/wllm/models/llama.py:443-446) and
 is evaluated only at the rows whose logits are wanted; logits are 32-bit.
 """
@@ -30,16 +32,26 @@ class ScaledEmbedding:
             scale = float(torch.tensor(scale, dtype=torch.float32))
         self.scale = scale
         self.table = None
+        self.position_name = spec.options.get("position_table")
+        self.max_positions = int(spec.max_positions) if self.position_name is not None else 0
+        self.position_table = None
 
     def param_specs(self):
-        return [ParamSpec(self.weight_name, (self.vocab, self.hidden_size), "table")]
+        out = [ParamSpec(self.weight_name, (self.vocab, self.hidden_size), "table")]
+        if self.position_name is not None:
+            out.append(ParamSpec(self.position_name, (self.max_positions, self.hidden_size), "table"))
+        return out
 
     def load(self, fetch):
         self.table = fetch(self.weight_name).contiguous()
+        if self.position_name is not None:
+            self.position_table = fetch(self.position_name).contiguous()
 
     def __call__(self, token_ids: torch.Tensor, ctx) -> torch.Tensor:
         out = ctx.buffer("residual", (token_ids.shape[0], self.hidden_size), torch.float32)
-        return ops.embed_gather(token_ids, self.table, self.scale, out)
+        if self.position_table is None:
+            return ops.embed_gather(token_ids, self.table, self.scale, out)
+        return ops.embed_gather(token_ids, self.table, self.scale, out, self.position_table, ctx.positions)
 
 
 @HEADS.register("logits_head")
@@ -51,6 +63,8 @@ class LogitsHead:
         self.weight_name = None if self.tied else spec.weight
         self.hidden_size, self.model_dtype, self.embedding = hidden_size, model_dtype, embedding
         self.weight = None
+        cap = spec.options.get("softcap")
+        self.softcap = None if cap is None else float(cap)
 
     def param_specs(self):
         return [] if self.tied else [ParamSpec(self.weight_name, (self.vocab, self.hidden_size), "table")]
@@ -61,4 +75,5 @@ class LogitsHead:
     def __call__(self, hidden_rows: torch.Tensor, ctx) -> torch.Tensor:
         if self.weight is None:
             self.weight = self.embedding.table
-        return ops.linear(hidden_rows, self.weight, f32_out=True)
+        logits = ops.linear(hidden_rows, self.weight, f32_out=True)
+        return logits if self.softcap is None else ops.tanh_cap(logits, self.softcap)

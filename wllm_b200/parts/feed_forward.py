@@ -1,8 +1,9 @@
 """Gated dense feed-forward: down(act(gate(x)) * up(x)).
 
 spec options: intermediate_size, activation ('gelu_tanh' for Gemma's GeGLU,
-src/wllm/models/gemma.py:54-62; 'silu'; 'relu'), gate_proj/up_proj/down_proj (checkpoint
-names).  gate and up are stored as one matrix [2 I, hidden] (gate rows first).  Under
+src/wllm/models/gemma.py:54-62; 'silu'; 'relu'; 'capped_swish' with `limit` and `slope`: the unit
+g = min(gate x, limit), u = clamp(up x, -limit, limit), down(g * sigmoid(slope g) * (u + 1))),
+gate_proj/up_proj/down_proj (checkpoint names).  gate and up are stored as one matrix [2 I, hidden] (gate rows first).  Under
 bfloat16 one tensor-memory GEMM computes both products and applies act(gate) * up in its
 epilogue, in 32-bit on the accumulators; otherwise one product feeds the activation kernel.
 """
@@ -20,8 +21,12 @@ class GatedDense:
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.inter = int(spec.intermediate_size)
         self.activation = spec.activation
-        if self.activation not in ("gelu_tanh", "silu", "relu"):
-            raise ValueError(f"activation {self.activation!r}: gelu_tanh, silu or relu")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r}: one of {', '.join(ops.ACTIVATIONS)}")
+        self.limit = float(spec.options.get("limit") or 0.0)
+        self.slope = float(spec.options.get("slope") or 0.0)
+        if self.activation == "capped_swish" and not (self.limit > 0 and self.slope > 0):
+            raise ValueError("activation capped_swish needs a positive limit and slope")
         self.hidden_size, self.model_dtype = hidden_size, model_dtype
         self.names = {k: spec.options[k] for k in ("gate_proj", "up_proj", "down_proj")}
         self.wgu = self.wd = None
@@ -38,5 +43,6 @@ class GatedDense:
     def __call__(self, x: torch.Tensor, ctx):
         n = x.shape[0]
         h = ops.gated_linear(x, self.wgu, self.activation, ctx.buffer("ffn_act", (n, self.inter), self.model_dtype),
-                             lambda shape, dtype: ctx.buffer("gate_up", shape, dtype))
+                             lambda shape, dtype: ctx.buffer("gate_up", shape, dtype),
+                             **({"limit": self.limit, "slope": self.slope} if self.activation == "capped_swish" else {}))
         return as_branch(ops.project(h, self.wd, lambda name, shape, dt: ctx.buffer("branch_" + name, shape, dt)))
