@@ -54,25 +54,32 @@ def visible(n, size, keep_first):
     return (j <= i) & ((i - j < size) | (j < keep_first))
 
 
+def _rot(m):
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    return rot["dims"], rot["base"]
+
+
 def keys_values(m, w, p, h):
     """Rotated keys [n, G, dim] and values [n, G, vdim] of the layer with prefix p from its input h."""
-    n = h.shape[0]
-    k = (h @ w[p + "k"].T).view(n, m["kv_heads"], m["dim"])
-    v = (h @ w[p + "v"].T).view(n, m["kv_heads"], m["vdim"])
-    return rotate_interleaved(k, torch.arange(n), m["rot"]["dims"], m["rot"]["base"]), v
+    n, G = h.shape[0], m.get("kv_heads", m["heads"])
+    k = (h @ w[p + "k"].T).view(n, G, m["dim"])
+    v = (h @ w[p + "v"].T).view(n, G, m.get("vdim", m["dim"]))
+    return rotate_interleaved(k, torch.arange(n), *_rot(m)), v
 
 
 def attention(m, w, p, h, kv):
     """m: the mixer's sizes; kv: (keys, values) as keys_values returns them (this layer's or another's)."""
-    n, H, G = h.shape[0], m["heads"], m["kv_heads"]
-    q = rotate_interleaved((h @ w[p + "q"].T).view(n, H, m["dim"]), torch.arange(n), m["rot"]["dims"], m["rot"]["base"])
+    n, H, G = h.shape[0], m["heads"], m.get("kv_heads", m["heads"])
+    q = rotate_interleaved((h @ w[p + "q"].T).view(n, H, m["dim"]), torch.arange(n), *_rot(m))
     k, v = kv
-    mask = visible(n, m["mask"]["size"], m["mask"]["keep_first"])
+    mask = visible(n, m["mask"]["size"], m["mask"].get("keep_first", 0)) if m.get("mask") else visible(n, n, 0)
+    scale = m["scale"] if m.get("scale") is not None else m["dim"] ** -0.5
     heads = []
     for a in range(H):
         g = a // (H // G)
-        s = (q[:, a] @ k[:, g].T) * m["scale"]
-        s = m["softcap"] * torch.tanh(s / m["softcap"])
+        s = (q[:, a] @ k[:, g].T) * scale
+        if m.get("softcap"):
+            s = m["softcap"] * torch.tanh(s / m["softcap"])
         s = s.masked_fill(~mask, float("-inf"))
         heads.append(torch.softmax(s, dim=-1) @ v[:, g])
     return torch.cat(heads, dim=-1) @ w[p + "o"].T
@@ -130,7 +137,13 @@ def forward(cfg, w, tokens, layers_out=None):
     """Logits [n, vocab] of one whole sequence; `layers_out` (a list) receives the sum of the streams after each layer."""
     eps = cfg["norm"]["eps"]
     x = embed(cfg, w, tokens)
-    streams = x[None].repeat(cfg["streams"], 1, 1)
+    bare = cfg.get("streams") is None                  # one plain residual: x <- x + sublayer(norm(x))
+    if bare:
+        w = dict(w)
+        for i, layer in enumerate(cfg["layers"]):
+            for q in ("hc1.", "hc2."):
+                w[f"l{i}.{q}in"], w[f"l{i}.{q}out"], w[f"l{i}.{q}mix"] = x.new_ones(1), x.new_ones(1), x.new_ones(1, 1)
+    streams = x[None].repeat(1 if bare else cfg["streams"], 1, 1)
     cache = {}
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
