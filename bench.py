@@ -23,6 +23,12 @@ is another workload (the default one and its line are unchanged): Pesanex models
 2,048-token prompt and decode at `batch` requests, device-timed; and the new design's kernels one by one at those
 shapes (L2 flushed before each timed launch), each with the bytes it must move over the measured copy bandwidth,
 beside the like kernel of the Gemma layer.  One JSON line.
+
+    python bench.py --design taritar [--steps K] [--warmup W] [--batch 8] [--context 2048] [--sizes 2k,4k]
+
+the same for Taritar (several residual streams, attention with a score cap behind a window that keeps first keys, layers
+that share keys and values, dense and routed feed-forwards): models of four layers at two real layer sizes beside a Gemma
+of equal width, dense feed-forward, heads and layers, and the design's kernels one by one beside their like kernels.
 """
 from __future__ import annotations
 
@@ -546,6 +552,199 @@ def pesanex_bench(args) -> int:
     return 0
 
 
+TARITAR_SIZES = {
+    # width, dense feed-forward, attention (heads, kv heads, head size), window, kept first keys, experts (count, top, ff, groups, kept groups), shared ff
+    "2k": dict(width=2048, ff=8192, attn=(16, 4, 128), window=1024, keep=4, experts=(32, 4, 1024, 4, 2), shared=2048, vocab=32000, layers=4),
+    "4k": dict(width=4096, ff=14336, attn=(32, 8, 128), window=2048, keep=4, experts=(64, 6, 1408, 8, 4), shared=2816, vocab=32000, layers=4),
+}
+
+
+def taritar_config(size: dict, streams: int = 2) -> dict:
+    """Four layers: dense, routed experts, dense on the keys and values of layer 0, routed experts on those of layer 1."""
+    nq, nkv, hd = size["attn"]
+    E, top, eff, groups, kept = size["experts"]
+
+    def mixer(src=None):
+        m = {"heads": nq, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
+             "rot": {"dims": hd // 2, "base": 1e6}, "mask": {"size": size["window"], "keep_first": size["keep"]}}
+        if src is not None:
+            m["kv_from"] = src
+        return m
+    dense = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": E, "top": top, "groups": {"count": groups, "keep": kept}},
+           "shared": {"ff": size["shared"], "limit": 7.0}}
+    layers = [{"type": "attention", "mixer": mixer(), "mlp": dense}, {"type": "attention", "mixer": mixer(), "mlp": moe},
+              {"type": "attention", "mixer": mixer(0), "mlp": dense}, {"type": "attention", "mixer": mixer(1), "mlp": moe}]
+    return {"architecture": "Taritar", "vocab": size["vocab"], "width": size["width"], "max_positions": 16384, "streams": streams,
+            "logit_softcap": 30.0, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": layers[:size["layers"]]}
+
+
+def taritar_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int) -> dict:
+    """Taritar's kernels alone at one size's shapes beside the like kernels of the Gemma layer: microseconds, the time the
+    bytes each must move (or its arithmetic) take at the measured peaks (`floor_us`), and how many times that it takes."""
+    import torch
+    from wllm_b200.kernels import ops
+    dev, bf, f32, i32 = "cuda:0", torch.bfloat16, torch.float32, torch.int32
+    flush = torch.zeros(160 << 20, dtype=f32, device=dev)
+    W = size["width"]
+    nq, nkv, hd = size["attn"]
+    E, top, eff, groups, kept = size["experts"]
+    window, keep = size["window"], size["keep"]
+    ps, S = 64, 2
+    out = {}
+
+    def row(name, fn, bytes_moved, flops=0.0):
+        us = timed_us(fn, flush)
+        floor = max(bytes_moved / (pk["hbm_gbs"] * 1e3), flops / (pk["bf16_tflops"] * 1e6))
+        out[name] = {"us": round(us, 1), "floor_us": round(floor, 2), "x_floor": round(us / max(floor, 1e-9), 1)}
+    g = torch.Generator(device=dev).manual_seed(1)
+
+    def rnd(*shape, dtype=f32, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev, dtype=f32) * scale).to(dtype)
+    # ---- the norm in front of a sublayer: Gemma's (residual += branch, norm) and the two-stream one (update, read, norm)
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        resid, delta, w = rnd(n, W), rnd(n, W, dtype=bf), rnd(W, dtype=bf)
+        o = torch.empty(n, W, dtype=bf, device=dev)
+        streams, gain = rnd(S, n, W), rnd(W)
+        mix, w_out, w_in = rnd(S, S), rnd(S), rnd(S)
+        row(f"{tag}/gemma rmsnorm+add", lambda: ops.rmsnorm(resid, delta, w, 1e-6, 1.0, o), n * W * (4 + 4 + 2 + 2))
+        row(f"{tag}/norm over {S} streams with their update", lambda: ops.hyper_norm(streams, streams, S, (delta, 0), mix, w_out, w_in, gain, 1e-6, o),
+            n * W * (8 * S + 2 + 2))
+    # ---- rotary + cache write: halves (Gemma) and interleaved pairs
+    pages = batch * (-(-(context + 1) // ps)) + -(-T // ps) + 1
+    kp, vp = rnd(pages, nkv, ps, hd, dtype=bf), rnd(pages, nkv, ps, hd, dtype=bf)
+    inv_freq = torch.arange(hd // 4, device=dev, dtype=f32).neg().div(hd // 4).exp()
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        qkv = rnd(n, (nq + 2 * nkv) * hd, dtype=bf)
+        qo = torch.empty(n, nq * hd, dtype=bf, device=dev)
+        pos = torch.arange(n, dtype=i32, device=dev)
+        moved = n * (nq + 2 * nkv) * hd * 2 * 2
+        row(f"{tag}/gemma rotary+cache write", lambda: ops.rope_kv_write(qkv, qo, pos, pos, inv_freq, kp, vp, nq, nkv, hd, hd // 2, ps), moved)
+        row(f"{tag}/rotary of interleaved pairs+cache write",
+            lambda: ops.rope_kv_write(qkv, qo, pos, pos, inv_freq, kp, vp, nq, nkv, hd, hd // 2, ps, pairing="interleaved"), moved)
+    # ---- attention: Gemma's over all keys; Taritar's with cap, window and kept keys (what a row sees is what is counted)
+    one = torch.ones(1, dtype=i32, device=dev)
+    table = torch.arange(-(-T // ps), dtype=i32, device=dev).view(1, -1)
+    q = rnd(T, nq * hd, dtype=bf)
+    ao = torch.empty(T, nq * hd, dtype=bf, device=dev)
+    seen = sum(min(p + 1, window + keep) for p in range(T))
+    row("prefill/gemma attention (all keys)", lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, 0,
+                                                                                 hd ** -0.5, skip_single=False), T * nq * hd * 4, 4.0 * nq * hd * T * T / 2)
+    row("prefill/gemma attention (window)", lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, window,
+                                                                               hd ** -0.5, skip_single=False), T * nq * hd * 4, 4.0 * nq * hd * seen)
+    from wllm_b200.parts.attention import PagedAttention  # noqa: F401  (the kernels below are the ones the mixer picks)
+    row("prefill/attention with cap, window and kept keys",
+        lambda: taritar_attention(ops, q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, window, hd ** -0.5, 30.0, keep, True),
+        T * nq * hd * 4, 4.0 * nq * hd * seen)
+    per = -(-(context + 1) // ps)
+    dtable = torch.arange(batch * per, dtype=i32, device=dev).view(batch, per)
+    qd, od = rnd(batch, nq * hd, dtype=bf), torch.empty(batch, nq * hd, dtype=bf, device=dev)
+    starts, lens = torch.arange(batch, dtype=i32, device=dev), torch.ones(batch, dtype=i32, device=dev)
+    ctxs = lens * context
+    split_keys, max_splits = ops.decode_split_plan(batch * nkv, -(-context // 512) * 512, 32 if hd % 64 == 0 else 64)
+    scratch = torch.empty(ops.attention_mma_scratch_floats(batch, nq, hd, max_splits), device=dev)
+    read = min(context, window + keep)
+    row("decode/gemma attention (all keys)", lambda: ops.attention_mma_decode(qd, od, kp, vp, starts, lens, ctxs, dtable, nq, nkv, hd, ps, 0, hd ** -0.5,
+                                                                               split_keys, max_splits, scratch), batch * context * nkv * hd * 2 * 2)
+    row("decode/gemma attention (window)", lambda: ops.attention_mma_decode(qd, od, kp, vp, starts, lens, ctxs, dtable, nq, nkv, hd, ps, window, hd ** -0.5,
+                                                                             split_keys, max_splits, scratch), batch * read * nkv * hd * 2 * 2)
+    row("decode/attention with cap, window and kept keys",
+        lambda: taritar_attention(ops, qd, od, kp, vp, starts, lens, ctxs, dtable, 1, nq, nkv, hd, ps, window, hd ** -0.5, 30.0, keep, False),
+        batch * read * nkv * hd * 2 * 2)
+    # ---- feed-forward: Gemma's dense unit; the clamped unit; the router, the plan and the grouped products of the experts
+    for n, tag in ((T, "prefill"), (batch, "decode")):
+        x = rnd(n, W, dtype=bf)
+        for ff, what in ((size["ff"], "dense"), (top * eff, "dense of the experts' total width")):
+            wgu, wd = rnd(2 * ff, W, dtype=bf, scale=0.02), rnd(W, ff, dtype=bf, scale=0.02)
+            act = torch.empty(n, ff, dtype=bf, device=dev)
+            gu = torch.empty(n, 2 * ff, dtype=bf, device=dev)
+            bytes_gu, bytes_d = 2 * ff * W * 2 + n * (W + ff) * 2, ff * W * 2 + n * (W + ff) * 2
+            if what == "dense":
+                row(f"{tag}/gemma gate|up with tanh-GELU", lambda: ops.gated_linear(x, wgu, "gelu_tanh", act, lambda sh, dt: gu), bytes_gu, 4.0 * n * ff * W)
+            row(f"{tag}/{what}: gate|up with the clamped unit", lambda: ops.gated_linear(x, wgu, "capped_swish", act, lambda sh, dt: gu, 7.0, 1.702),
+                bytes_gu, 4.0 * n * ff * W)
+            parts = {}
+            row(f"{tag}/{what}: down", lambda: ops.project(act, wd, lambda name, sh, dt: parts.setdefault((name, sh), torch.empty(sh, dtype=dt, device=dev))),
+                bytes_d, 2.0 * n * ff * W)
+        wr, wg = rnd(E, W, scale=0.05), rnd(W, scale=0.05)
+        chosen, weights, gate = torch.empty(n, top, dtype=i32, device=dev), torch.empty(n, top, device=dev), torch.empty(n, device=dev)
+        row(f"{tag}/router (scores, groups, choice, shared gate)", lambda: ops.moe_route(x, wr, wg, chosen, weights, gate, groups, kept),
+            n * W * 2 + (E + 1) * W * 4)
+        pairs = n * top
+        count, offset = torch.empty(E, dtype=i32, device=dev), torch.empty(E + 1, dtype=i32, device=dev)
+        order, place = torch.empty(pairs, dtype=i32, device=dev), torch.empty(pairs, dtype=i32, device=dev)
+        row(f"{tag}/pairs sorted by expert", lambda: ops.moe_plan(chosen, count, offset, order, place), pairs * 4 * 3)
+        w_gu, w_d = rnd(E, 2 * eff, W, dtype=bf, scale=0.02), rnd(E, W, eff, dtype=bf, scale=0.02)
+        act, y = torch.empty(pairs, eff, dtype=bf, device=dev), torch.empty(pairs, W, device=dev)
+        used = min(E, pairs)           # experts whose weights a step reads at most
+        row(f"{tag}/experts: gate|up with the clamped unit (grouped)", lambda: ops.moe_grouped(x, w_gu, act, offset, order, top, True, 7.0, 1.702),
+            used * 2 * eff * W * 2 + pairs * (W + eff) * 2, 4.0 * pairs * eff * W)
+        row(f"{tag}/experts: down (grouped)", lambda: ops.moe_grouped(act, w_d, y, offset, order, top, False),
+            used * eff * W * 2 + pairs * (eff * 2 + W * 4), 2.0 * pairs * eff * W)
+        shared, o32 = rnd(n, W, dtype=bf), torch.empty(n, W, device=dev)
+        row(f"{tag}/experts' outputs weighted and summed, shared unit gated and added", lambda: ops.moe_combine(y, place, weights, (shared, 0), gate, o32),
+            pairs * W * 4 + n * W * (2 + 4))
+    # ---- embedding with a position row; capped logits
+    emb, pos_table = rnd(size["vocab"], W, dtype=bf), rnd(4096, W, dtype=bf)
+    ids = torch.randint(0, size["vocab"], (T,), generator=g, device=dev, dtype=i32)
+    at = torch.arange(T, dtype=i32, device=dev)
+    r32 = torch.empty(T, W, device=dev)
+    row("prefill/gemma embedding", lambda: ops.embed_gather(ids, emb, 1.0, r32), T * W * (2 + 4))
+    row("prefill/embedding with position rows", lambda: ops.embed_gather(ids, emb, 1.0, r32, pos_table, at), T * W * (2 + 2 + 4))
+    logits = rnd(batch, size["vocab"])
+    row("decode/tanh cap of the logits", lambda: ops.tanh_cap(logits, 30.0), batch * size["vocab"] * 8)
+    return out
+
+
+def taritar_attention(ops, q, out, kp, vp, starts, lens, ctxs, table, max_q_len, nq, nkv, hd, ps, window, scale, cap, keep, multi):
+    """The launches that the attention mixer makes for a step of bfloat16 rows with a cap and kept keys (parts/attention.py)."""
+    import torch
+    from wllm_b200.parts.attention import capped_attention_launch
+    capped_attention_launch(ops, q, out, kp, vp, starts, lens, ctxs, table, max_q_len, nq, nkv, hd, ps, window, scale, cap, keep, multi)
+
+
+def taritar_bench(args) -> int:
+    import torch
+    from wllm_b200.config import EngineConfig, GemmaConfig, TaritarConfig
+    from wllm_b200.engine import build_model
+    pk = peaks()
+    ps, T = args.page_size, 2048
+    context = args.context or 2048
+    engine_cfg = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=max(64, args.batch), cuda_graphs=not args.no_graphs)
+    sizes = {}
+    for name in (args.sizes if args.sizes != "2b,7b" else "2k,4k").split(","):
+        size = TARITAR_SIZES[name]
+        nq, nkv, hd = size["attn"]
+        models = {
+            "gemma": GemmaConfig.from_dict(dict(architectures=["GemmaForCausalLM"], vocab_size=size["vocab"], hidden_size=size["width"],
+                                                intermediate_size=size["ff"], num_hidden_layers=size["layers"],
+                                                num_attention_heads=nq, num_key_value_heads=nkv, head_dim=hd,
+                                                max_position_embeddings=16384)),
+            "taritar": TaritarConfig.from_dict(taritar_config(size)),
+        }
+        res = {}
+        for label, cfg in models.items():
+            model = build_model(None, engine_cfg.dtype, engine_cfg.device, config=cfg, random_seed=1)
+            pre_ms = prefill_run(model, engine_cfg, T, ps)
+            ms, launches, _, clocks, _ = decode_run(model, engine_cfg, args.batch, context, min(args.steps, 32), args.warmup, ps, 3)
+            res[label] = {"weights_gb": round(model.weight_bytes() / 1e9, 3), "prefill_tok_s": round(T / (pre_ms / 1e3), 1),
+                          "prefill_ms": round(pre_ms, 3), "decode_tok_s": round(args.batch / (ms / 1e3), 1),
+                          "decode_ms_per_step": round(ms, 4), "decode_launches": launches, "clocks": clocks}
+            del model
+            torch.cuda.empty_cache()
+        sizes[name] = {"shape": size, "models": res}
+        if not args.no_points:
+            sizes[name]["kernels"] = taritar_kernel_table(size, pk, T, args.batch, context)
+    print(json.dumps({"metric": "Taritar beside Gemma at equal layer sizes: prefill tok/s @ 2048 tokens, decode tok/s",
+                      "design": "taritar", "unit": "tokens/s", "n_gpus": 1, "steps": min(args.steps, 32), "warmup": args.warmup,
+                      "dtype": "bf16", "data": "synthetic (random weights, random token ids, random cached keys/values)",
+                      "config": {"global_batch": args.batch, "seq_len": context, "prefill_tokens": T, "page_size": ps,
+                                 "cuda_graphs": not args.no_graphs, "peaks": pk["source"],
+                                 "l2": "kernel table: a 640 MB buffer is written before every timed launch"},
+                      "peaks": pk, "sizes": sizes}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -560,8 +759,8 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
-    ap.add_argument("--design", default="gemma", choices=["gemma", "pesanex"],
-                    help="gemma: the default workload; pesanex: Pesanex models beside a Gemma of equal layer sizes (another line)")
+    ap.add_argument("--design", default="gemma", choices=["gemma", "pesanex", "taritar"],
+                    help="gemma: the default workload; pesanex, taritar: models of that design beside a Gemma of equal layer sizes (another line)")
     ap.add_argument("--sizes", default="2b,7b", help="--design pesanex: which of the layer sizes to run (2b, 7b)")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -572,6 +771,8 @@ def main() -> int:
         return reference_arm(args)
     if args.design == "pesanex":
         return pesanex_bench(args)
+    if args.design == "taritar":
+        return taritar_bench(args)
     import torch
     from wllm_b200.config import EngineConfig, GemmaConfig
     from wllm_b200.engine import build_model

@@ -378,3 +378,63 @@ def test_experts_as_grouped_products(n, E, top, H, I, dtype):
     few = ops.moe_combine(y, place[:m * top], weights[:m].contiguous().to(DEV), (shared[:, :m].contiguous().to(DEV), 2),
                           gate[:m].contiguous().to(DEV), torch.empty(m, H, device=DEV))
     assert torch.equal(few.cpu(), out.cpu()[:m])
+
+
+@pytest.mark.parametrize("hd", [32, 48, 64, 128])
+@pytest.mark.parametrize("size,keep,cap", [(40, 5, 6.0), (96, 33, 0.0), (16, 16, 20.0), (8, 70, 4.0), (64, 0, 2.5), (130, 1, 0.0), (100, 64, 3.0)])
+def test_tensor_core_attention_with_a_cap_and_kept_first_keys(size, keep, cap, hd):
+    """The bfloat16 kernels on mma.sync that walk a list of key tiles (the kept keys' tiles, then the window's): a prompt's
+    portion and decoded rows, with one key standing out at every edge, pages in scrambled order, page sizes 16 and 64, keys
+    cut into several splits."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(size * 7 + keep + hd)
+    H, G, L, dtype = 4, 2, 300, torch.bfloat16
+    scale = 0.4 * (16 / hd) ** 0.5
+    k = torch.randn(L, G, hd, generator=g).to(dtype)
+    v = torch.randn(L, G, hd, generator=g).to(dtype)
+    n0 = 236
+    positions = list(range(n0, L))
+    q = torch.randn(len(positions), H, hd, generator=g).to(dtype)
+    one = lambda x: torch.tensor([x], dtype=torch.int32, device=DEV)
+    edges = sorted({e for e in (keep - 1, keep, 0, n0 - size, n0 - size + 1, L - 1 - size, L - size, 63, 64, 127, 128) if 0 <= e < L})
+    for ps in (16, 64):
+        for edge in edges:
+            k2 = k.clone()
+            k2[edge] = (q[0, 0::2] * 6).to(dtype)
+            kp, vp, table = paged(k2, v, ps, 5 + ps)
+            want = plain_attention_rows(q, k2, v, positions, scale, cap, size, keep)
+            qd = q.reshape(len(positions), H * hd).to(DEV)
+            out = torch.empty(len(positions), H * hd, dtype=dtype, device=DEV)
+            ops.attention_mma_prefill(qd, out, kp, vp, one(0), one(len(positions)), one(L), table, len(positions), H, G, hd, ps, size,
+                                      scale, skip_single=False, cap=cap, keep=keep)
+            err = (out.cpu().double() - want).abs().max()
+            assert err < 0.03, ("prefill", ps, edge, float(err))
+            # the last three rows as decoded tokens of three requests of different lengths on the same pages
+            R = 3
+            tables = table.expand(R, -1).contiguous()
+            starts = torch.arange(R, dtype=torch.int32, device=DEV)
+            lens = torch.ones(R, dtype=torch.int32, device=DEV)
+            ctxs = torch.tensor([L - 2, L - 1, L], dtype=torch.int32, device=DEV)
+            for split_keys, max_splits in ((512, 1), (128, 3), (64, 5)):
+                scratch = torch.empty(ops.attention_mma_scratch_floats(R, H, hd, max_splits), device=DEV)
+                od = torch.empty(R, H * hd, dtype=dtype, device=DEV)
+                ops.attention_mma_decode(qd[-3:].contiguous(), od, kp, vp, starts, lens, ctxs, tables, H, G, hd, ps, size, scale,
+                                         split_keys, max_splits, scratch, cap=cap, keep=keep)
+                err = (od.cpu().double() - want[-3:]).abs().max()
+                assert err < 0.03, ("decode", ps, edge, split_keys, float(err))
+    assert ops.tc_gemm_status(DEV) == 0
+
+
+@pytest.mark.parametrize("M", [3, 70, 300])
+def test_the_clamped_unit_in_the_products_epilogue(M):
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(M)
+    K, I, limit, slope = 96, 160, 0.7, 1.702
+    a = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(2 * I, K, generator=g) * 0.15).bfloat16()
+    out = ops.gated_linear(a.to(DEV), w.to(DEV), "capped_swish", torch.empty(M, I, dtype=torch.bfloat16, device=DEV),
+                           lambda shape, dtype: torch.empty(shape, dtype=dtype, device=DEV), limit, slope)
+    gate, up = (a.double() @ w.double()[:I].T).clamp(max=limit), (a.double() @ w.double()[I:].T).clamp(-limit, limit)
+    want = gate * torch.sigmoid(slope * gate) * (up + 1)
+    assert (out.cpu().double() - want).abs().max() < 0.02 and float((a.double() @ w.double()[:I].T > limit).float().mean()) > 0.1
+    assert ops.tc_gemm_status(DEV) == 0

@@ -112,10 +112,10 @@ template <int NT>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, const bf16* __restrict__ k_pages,
                                              const bf16* __restrict__ v_pages, const int* __restrict__ table,
                                              int tile_start, int key_lo, int key_hi, int g, int nkv, int page_size,
-                                             int page_shift) {
+                                             int page_shift, int kept_lo = 0, int kept_hi = 0) {
     const int lane = threadIdx.x & 31;
     const int first_page = tile_start >> page_shift;
-    const int last_page = (min(tile_start + BN, key_hi) - 1) >> page_shift;
+    const int last_page = (min(tile_start + BN, max(key_hi, kept_hi)) - 1) >> page_shift;
     int my_page = 0;
     if (first_page + lane <= last_page) my_page = table[first_page + lane];
 #pragma unroll
@@ -125,7 +125,7 @@ __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, con
         const int key = tile_start + row;
         const int page = __shfl_sync(0xffffffffu, my_page, ((key >> page_shift) - first_page) & 31);
         if (BN * CPR % NT != 0 && idx >= BN * CPR) continue;
-        const bool valid = key >= key_lo && key < key_hi;
+        const bool valid = (key >= key_lo && key < key_hi) || (key >= kept_lo && key < kept_hi);
         const size_t off = valid ? ((size_t)(page * nkv + g) * page_size + (key & (page_size - 1))) * HD + chunk * 8 : 0;
         cp_async16(k_dst + swz<BN>(row, chunk), k_pages + off, valid);
         cp_async16(v_dst + swz<BN>(row, chunk), v_pages + off, valid);
@@ -177,9 +177,12 @@ struct RowState {
 // One warp: its 16 query rows (at q_rows in shared memory) against NKEYS keys of a tile
 // that start at shared-memory row `key0`; `pos_r[i]`/`first_r[i]` bound the keys each of the
 // thread's two rows may see; `key_base` is the absolute index of tile row 0.
+// `kept_r[i]` / `kept_lo`: keys kept_lo <= key < kept_r[i] are seen as well although they lie before first_r[i] (a sequence's
+// first keys that stay visible behind a window); `capl` > 0: scores (log2 units) become capl * tanh(score / capl).
 template <int NKEYS, int QROWS, int KROWS = BN>
 __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_row0, uint32_t k_tile, uint32_t v_tile, int key0,
-                                          int key_base, const int (&pos_r)[2], const int (&first_r)[2], float scale2) {
+                                          int key_base, const int (&pos_r)[2], const int (&first_r)[2], float scale2,
+                                          const int (&kept_r)[2], int kept_lo, float capl) {
     constexpr int NT = NKEYS / 8;
     const int lane = threadIdx.x & 31;
     float s[NT][4];
@@ -207,8 +210,10 @@ __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_r
         for (int c = 0; c < 4; ++c) {
             const int key = key_base + key0 + n * 8 + (lane & 3) * 2 + (c & 1);
             const int i = c >> 1;
-            const bool ok = key <= pos_r[i] && key >= first_r[i];
-            s[n][c] = ok ? s[n][c] * scale2 : -INFINITY;
+            const bool ok = key <= pos_r[i] && (key >= first_r[i] || (key < kept_r[i] && key >= kept_lo));
+            float v = s[n][c] * scale2;
+            if (capl > 0.f) v = capl * tanhf(v / capl);
+            s[n][c] = ok ? v : -INFINITY;
             mx[i] = fmaxf(mx[i], s[n][c]);
         }
     float corr[2], base[2];
@@ -253,6 +258,13 @@ __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_r
     }
 }
 
+template <int NKEYS, int QROWS, int KROWS = BN>
+__device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_row0, uint32_t k_tile, uint32_t v_tile, int key0,
+                                          int key_base, const int (&pos_r)[2], const int (&first_r)[2], float scale2) {
+    const int none[2] = {0, 0};
+    warp_tile<NKEYS, QROWS, KROWS>(st, q_tile, q_row0, k_tile, v_tile, key0, key_base, pos_r, first_r, scale2, none, 0, 0.f);
+}
+
 __device__ __forceinline__ void init_state(RowState& st) {
     st.m[0] = st.m[1] = -INFINITY;
     st.l[0] = st.l[1] = 0.f;
@@ -274,9 +286,22 @@ struct TileRing {
     const int* table;
     int max_pages, key_lo, key_hi, g, nkv, page_size, page_shift, t0, t1;
     int ctx_end;                  // the request's keys end here: rows of a box copy from here on hold no key
+    // A sequence's kept first keys [kept_lo, kept_hi) that lie before key_lo are read as well: the `h` tiles from tile h0
+    // that hold them (and come before tile t0) are walked first.  Place n of the walk is tile h0 + n, or t0 + n - h.
+    int kept_lo = 0, kept_hi = 0, h0 = 0, h = 0;
 
     __device__ __forceinline__ uint32_t k_stage(int s) const { return kv_s + (2 * s) * TILE_BYTES; }
     __device__ __forceinline__ uint32_t v_stage(int s) const { return kv_s + (2 * s + 1) * TILE_BYTES; }
+    __device__ __forceinline__ int count() const { return h + max(t1 - t0, 0); }
+    __device__ __forceinline__ int tile_of(int n) const { return n < h ? h0 + n : t0 + n - h; }
+    // the kept keys of this walk, given the range [lo, hi) that the CTA is responsible for
+    __device__ __forceinline__ void keep(int keep_first, int lo, int hi) {
+        kept_lo = lo; kept_hi = min(min(hi, keep_first), key_lo);
+        if (kept_hi <= kept_lo) { kept_lo = kept_hi = 0; h = 0; return; }
+        h0 = kept_lo / BN;
+        h = min((kept_hi + BN - 1) / BN, t1 > t0 ? t0 : (kept_hi + BN - 1) / BN) - h0;
+        if (h < 0) h = 0;
+    }
 
     __device__ __forceinline__ void init() {
         if (USE_TMA) {
@@ -288,45 +313,48 @@ struct TileRing {
             __syncthreads();
         }
     }
-    __device__ __forceinline__ void issue(int t) {      // tile t into its stage
-        const int s = (t - t0) % STAGES;
+    __device__ __forceinline__ void issue(int n) {      // the tile at place n into its stage
+        const int s = n % STAGES, t = tile_of(n);
         if (USE_TMA) {
-            if (threadIdx.x == 0 && t < t1)
+            if (threadIdx.x == 0 && n < count())
                 tma_kv_tile(k_stage(s), v_stage(s), bars + 8 * s, k_map, v_map, table, max_pages, t * BN, g, nkv, page_size,
                             page_shift);
         } else {
-            if (t < t1)
+            if (n < count())
                 load_kv_tile<NT>(k_stage(s), v_stage(s), k_pages, v_pages, table, t * BN, key_lo, key_hi, g, nkv, page_size,
-                                 page_shift);
+                                 page_shift, kept_lo, kept_hi);
             cp_commit();
         }
     }
     __device__ __forceinline__ void prologue() {
-        for (int s = 0; s < STAGES - 1; ++s) issue(t0 + s);
+        for (int s = 0; s < STAGES - 1; ++s) issue(s);
     }
     // false (for every thread of the CTA alike) if the tile did not arrive within the limit (TMA only)
-    __device__ __forceinline__ bool arrive(int t) {
+    __device__ __forceinline__ bool arrive(int n) {
         int ok = 1;
         if (USE_TMA) {
-            const int n = t - t0;
+            const int t = tile_of(n);
             ok = mbar_wait(bars + 8 * (n % STAGES), (n / STAGES) & 1) ? 1 : 0;
             if (ok && t * BN + BN > ctx_end)
                 zero_value_rows<BN>(v_stage(n % STAGES), HD / 64, max(0, ctx_end - t * BN), BN, threadIdx.x, NT);
-            if (ok && t * BN < key_lo)
-                zero_value_rows<BN>(v_stage(n % STAGES), HD / 64, 0, min(BN, key_lo - t * BN), threadIdx.x, NT);
+            if (ok && n < h) {
+                if (kept_hi - t * BN < BN)           // behind the kept keys: whatever the (perhaps released) pages hold
+                    zero_value_rows<BN>(v_stage(n % STAGES), HD / 64, max(0, kept_hi - t * BN), BN, threadIdx.x, NT);
+            } else if (ok && t * BN < key_lo) {
+                zero_value_rows<BN>(v_stage(n % STAGES), HD / 64, min(BN, max(0, kept_hi - t * BN)), min(BN, key_lo - t * BN), threadIdx.x, NT);
+            }
         } else {
             cp_wait<STAGES - 2>();
         }
         ok = __syncthreads_and(ok);
-        if (ok) issue(t + STAGES - 1);
+        if (ok) issue(n + STAGES - 1);
         return ok != 0;
     }
     // Nothing of this CTA's copies may be in flight when it leaves.  After a normal run that is so already;
-    // after giving up on tile `failed`, the tiles issued behind it are waited for, again with the limit.
+    // after giving up at place `failed`, the tiles issued behind it are waited for, again with the limit.
     __device__ __forceinline__ void drain(int failed) {
         if (USE_TMA) {
-            for (int t = failed + 1; failed >= 0 && t < min(t1, failed + STAGES - 1); ++t) {
-                const int n = t - t0;
+            for (int n = failed + 1; failed >= 0 && n < min(count(), failed + STAGES - 1); ++n) {
                 if (!mbar_wait(bars + 8 * (n % STAGES), (n / STAGES) & 1)) break;
             }
         } else {
@@ -366,13 +394,15 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
               const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
               const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
               int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status,
-              const float* __restrict__ sinks) {
+              const float* __restrict__ sinks, float capl, int keep) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     const int split = blockIdx.z, g = blockIdx.y, r = blockIdx.x;     // CTAs start request by request, the last (shortest) splits last
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    int first = window > 0 ? max(0, pos - window + 1) : 0;
+    int kept = 0;               // the sequence's first keys that stay visible behind the window (none, or the two runs touch)
+    if (keep > 0) { if (first <= keep) first = 0; else kept = keep; }
     const int part_keys = keys_per_split(ctx, split_keys, max_splits, SPLIT_TILE);
     const int num_splits = (ctx + part_keys - 1) / part_keys;
     if (split >= num_splits) return;
@@ -395,6 +425,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     ring.page_shift = 31 - __clz(page_size);
     ring.t0 = key_lo / BN; ring.t1 = empty ? ring.t0 : (key_hi + BN - 1) / BN;
     ring.ctx_end = ctx;
+    ring.keep(kept, split * part_keys, (split + 1) * part_keys);
     ring.init();
     load_q_tile<NTHREADS, 16>(q_s, q, q_stride, token, 1, 0, 16, g, rep);
     if (USE_TMA) cp_commit();
@@ -402,12 +433,14 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     if (USE_TMA) cp_wait<0>();               // the query tile (cp.async); the first arrive() synchronises the CTA
     const int first_r[2] = {key_lo, key_lo};
     const int hi_r[2] = {min(pos, key_hi - 1), min(pos, key_hi - 1)};
-    int t = ring.t0;
+    const int kept_r[2] = {ring.kept_hi, ring.kept_hi};
+    int t = 0;                  // place in the ring's walk
     bool ok = true;
-    for (; t < ring.t1; ++t) {
+    for (; t < ring.count(); ++t) {
         if (!ring.arrive(t)) { ok = false; break; }
-        const int s = (t - ring.t0) % DEC_STAGES;
-        warp_tile<16, 16>(st, q_s, 0, ring.k_stage(s), ring.v_stage(s), warp * 16, t * BN, hi_r, first_r, scale2);
+        const int s = t % DEC_STAGES;
+        warp_tile<16, 16>(st, q_s, 0, ring.k_stage(s), ring.v_stage(s), warp * 16, ring.tile_of(t) * BN, hi_r, first_r, scale2,
+                          kept_r, ring.kept_lo, capl);
     }
     ring.drain(ok ? -1 : t);
     if (!ok) {
@@ -733,7 +766,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
-               int skip_single, int* __restrict__ status, const float* __restrict__ sinks) {
+               int skip_single, int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     const int g = blockIdx.x, r = blockIdx.y;                 // grid (key/value heads, requests, tiles): the longest tiles start first
@@ -752,14 +785,19 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     const int last_row = min(rows, row0 + BM) - 1;
     const int pos_hi = pos0 + last_row / rep;
     const int pos_lo = pos0 + row0 / rep;
-    const int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, key_hi = pos_hi + 1;
+    int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, kept_cta = 0;
+    const int key_hi = pos_hi + 1;
+    // a sequence's first `keep` keys stay visible behind the window; where they touch the window there is one run from 0
+    if (keep > 0) { if (key_lo <= keep) key_lo = 0; else kept_cta = keep; }
 
-    int pos_r[2], first_r[2];
+    int pos_r[2], first_r[2], kept_r[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int m = row0 + warp * 16 + (lane >> 2) + i * 8;
         pos_r[i] = m < rows ? pos0 + m / rep : -1;                      // a row past the end sees no key
         first_r[i] = window > 0 ? max(0, pos_r[i] - window + 1) : 0;
+        kept_r[i] = 0;
+        if (keep > 0) { if (first_r[i] <= keep) first_r[i] = 0; else kept_r[i] = keep; }
     }
     RowState st;
     init_state(st);
@@ -771,20 +809,21 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     ring.page_shift = 31 - __clz(page_size);
     ring.t0 = key_lo / BN; ring.t1 = (key_hi + BN - 1) / BN;
     ring.ctx_end = ctx;
+    ring.keep(kept_cta, 0, key_hi);
     ring.init();
     load_q_tile<PRE_THREADS, BM>(q_s, q, q_stride, q_start, q_len, row0, BM, g, rep);
     if (USE_TMA) cp_commit();
     ring.prologue();
     if (USE_TMA) cp_wait<0>();
-    int t = ring.t0;
+    int t = 0;                  // place in the ring's walk
     bool ok = true;
-    for (; t < ring.t1; ++t) {
+    for (; t < ring.count(); ++t) {
         if (!ring.arrive(t)) { ok = false; break; }
-        const int s = (t - ring.t0) % PRE_STAGES;
+        const int s = t % PRE_STAGES, tile = ring.tile_of(t);
         // a warp whose rows all end before this tile has nothing to add
         const int warp_hi = pos0 + min(rows - 1, row0 + warp * 16 + 15) / rep;
-        if (t * BN <= warp_hi && row0 + warp * 16 < rows)
-            warp_tile<BN, BM>(st, q_s, warp * 16, ring.k_stage(s), ring.v_stage(s), 0, t * BN, pos_r, first_r, scale2);
+        if (tile * BN <= warp_hi && row0 + warp * 16 < rows)
+            warp_tile<BN, BM>(st, q_s, warp * 16, ring.k_stage(s), ring.v_stage(s), 0, tile * BN, pos_r, first_r, scale2, kept_r, 0, capl);
     }
     ring.drain(ok ? -1 : t);
     if (!ok) {
@@ -907,13 +946,17 @@ static int check_common(const void* q, int q_stride, const void* out, int out_st
 // `pool_pages` is the number of pages of k_pages / v_pages; `status` is a device int that stays 0 unless
 // a CTA gave up waiting for a tile.
 // `sinks` (null: none): one 32-bit number per query head, one more term e^sink of every row's softmax denominator.
-WLLM_API int wllm_attention_mma_decode_sinks(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                             const void* v_pages, long long pool_pages, const int* req_q_start,
-                                             const int* req_q_len, const int* req_ctx_len, const int* block_table,
-                                             int max_pages, int requests, int nq, int nkv, int page_size, int window,
-                                             float scale, int split_keys, int max_splits, float* scratch, int* status,
-                                             const float* sinks, cudaStream_t stream) {
+// `cap` > 0: scores become cap * tanh(score / cap); `keep` > 0 (with a window): the sequence's first keys stay visible
+// behind the window.  Either sends the launch to the kernel that walks a list of tiles (decode_kernel), at every head size.
+WLLM_API int wllm_attention_mma_decode_capped(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                              const void* v_pages, long long pool_pages, const int* req_q_start,
+                                              const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                              int max_pages, int requests, int nq, int nkv, int page_size, int window,
+                                              float scale, int split_keys, int max_splits, float* scratch, int* status,
+                                              const float* sinks, float cap, int keep, cudaStream_t stream) {
     if (requests <= 0) return WLLM_OK;
+    if (cap < 0.f || keep < 0 || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
+    const bool listed = cap > 0.f || keep > 0;
     const int bad = check_common(q, q_stride, out, out_stride, k_pages, v_pages, nq, nkv, page_size, pool_pages);
     if (bad) return bad;
     const int tile = USE_TMA ? WS_BN : BN;      // splits are whole tiles of the kernel that runs
@@ -930,9 +973,8 @@ WLLM_API int wllm_attention_mma_decode_sinks(const void* q, int q_stride, void* 
     if (r) return r;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = USE_TMA
-            ? cudaFuncSetAttribute(decode_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM)
-            : cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        if (e == cudaSuccess && USE_TMA) e = cudaFuncSetAttribute(decode_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM);
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
@@ -940,7 +982,7 @@ WLLM_API int wllm_attention_mma_decode_sinks(const void* q, int q_stride, void* 
     float* part_ml = scratch + (size_t)requests * nq * max_splits * HD;
     if ((long long)requests * nkv * max_splits <= 148) split_keys = -split_keys;     // resident at once: cut evenly
     int st;
-    if (USE_TMA)
+    if (USE_TMA && !listed)
         st = wllm_launch(decode_ws_kernel, dim3(requests, nkv, max_splits), WS_THREADS, WS_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                          block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys, max_splits, part_o,
@@ -949,11 +991,22 @@ WLLM_API int wllm_attention_mma_decode_sinks(const void* q, int q_stride, void* 
         st = wllm_launch(decode_kernel, dim3(requests, nkv, max_splits), NTHREADS, DEC_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                          req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window,
-                         scale * LOG2E, split_keys, max_splits, part_o, part_ml, status, sinks);
+                         scale * LOG2E, split_keys, max_splits, part_o, part_ml, status, sinks, cap * LOG2E, keep);
     if (st || max_splits == 1) return st;
     return wllm_launch(merge_kernel, dim3(nq, requests), HD >= 256 ? 256 : (HD >= 128 ? 128 : 64), 0, stream,
                        (bf16*)out, out_stride, req_q_start, req_q_len, req_ctx_len, nq, split_keys, max_splits,
                        (const float*)part_o, (const float*)part_ml, sinks);
+}
+
+WLLM_API int wllm_attention_mma_decode_sinks(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                             const void* v_pages, long long pool_pages, const int* req_q_start,
+                                             const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                             int max_pages, int requests, int nq, int nkv, int page_size, int window,
+                                             float scale, int split_keys, int max_splits, float* scratch, int* status,
+                                             const float* sinks, cudaStream_t stream) {
+    return wllm_attention_mma_decode_capped(q, q_stride, out, out_stride, k_pages, v_pages, pool_pages, req_q_start, req_q_len,
+                                            req_ctx_len, block_table, max_pages, requests, nq, nkv, page_size, window, scale,
+                                            split_keys, max_splits, scratch, status, sinks, 0.f, 0, stream);
 }
 
 WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
@@ -974,12 +1027,15 @@ WLLM_API long long wllm_attention_mma_prefill_halves_floats(int requests, int ma
 }
 
 // Tokens of requests with q_len > 1 (and of those with q_len == 1 too unless skip_single).
-WLLM_API int wllm_attention_mma_prefill_sinks(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                              const void* v_pages, long long pool_pages, const int* req_q_start,
-                                              const int* req_q_len, const int* req_ctx_len, const int* block_table,
-                                              int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
-                                              int window, float scale, int skip_single, int split_above, float* halves,
-                                              int* status, const float* sinks, cudaStream_t stream) {
+// `cap`, `keep`: as for decode; either sends the launch to the kernel that walks a list of tiles (prefill_kernel).
+WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                               const void* v_pages, long long pool_pages, const int* req_q_start,
+                                               const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                               int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
+                                               int window, float scale, int skip_single, int split_above, float* halves,
+                                               int* status, const float* sinks, float cap, int keep, cudaStream_t stream) {
+    if (cap < 0.f || keep < 0 || (keep > 0 && window <= 0)) return WLLM_BAD_SIZE;
+    const bool listed = cap > 0.f || keep > 0;
     // split_above > 0 (tensor-memory kernel only): a tile of 128 rows that walks more than split_above tiles of
     // 64 keys is shared by two CTAs; `halves` then holds wllm_attention_mma_prefill_halves_floats(...) floats.
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
@@ -1020,14 +1076,14 @@ WLLM_API int wllm_attention_mma_prefill_sinks(const void* q, int q_stride, void*
 #if (HEAD_DIM % 64 == 0)
 #if (HEAD_DIM % 128 == 0)
     // more than one tile of 128 rows in the longest request: pairs of CTAs on 256-row tiles
-    if (use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+    if (!listed && use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         const int pair_tiles = (max_q_len * (nq / nkv) + 2 * TC_BM - 1) / (2 * TC_BM);
         return wllm_launch(prefill_pair_kernel, dim3(2 * nkv, requests, pair_tiles), TC_THREADS, PR_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                            block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status, sinks);
     }
 #endif
-    if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+    if (!listed && use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         int* arrivals = nullptr;
         if (split_above > 0) {
             if (halves == nullptr || ((uintptr_t)halves & 15) || (long long)tiles * nkv * requests > ARRIVAL_SLOTS) return WLLM_BAD_SIZE;
@@ -1043,7 +1099,18 @@ WLLM_API int wllm_attention_mma_prefill_sinks(const void* q, int q_stride, void*
     return wllm_launch(prefill_kernel, dim3(nkv, requests, tiles), PRE_THREADS, PRE_SMEM, stream,
                        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                        req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E,
-                       skip_single, status, sinks);
+                       skip_single, status, sinks, cap * LOG2E, keep);
+}
+
+WLLM_API int wllm_attention_mma_prefill_sinks(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                              const void* v_pages, long long pool_pages, const int* req_q_start,
+                                              const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                              int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
+                                              int window, float scale, int skip_single, int split_above, float* halves,
+                                              int* status, const float* sinks, cudaStream_t stream) {
+    return wllm_attention_mma_prefill_capped(q, q_stride, out, out_stride, k_pages, v_pages, pool_pages, req_q_start, req_q_len,
+                                             req_ctx_len, block_table, max_pages, requests, max_q_len, nq, nkv, page_size,
+                                             window, scale, skip_single, split_above, halves, status, sinks, 0.f, 0, stream);
 }
 
 WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -41,7 +41,10 @@ template <int AROWS> struct Ring {
 };
 constexpr int NUM_THREADS = 192;
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3, EPI_GATED_RELU = 4 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3, EPI_GATED_RELU = 4, EPI_GATED_CAPPED = 5 };
+__host__ __device__ constexpr bool epi_gated(int e) { return e >= EPI_GATED_GELU; }
+// The gated epilogues' constants (EPI_GATED_CAPPED alone reads them: limit, slope), passed by value down to the drain.
+struct EpiParams { float p0, p1; };
 // With k_splits > 1 (32-bit output only) the K range is cut into k_splits parts of whole 64-column
 // blocks; part s of a tile is a work item of its own and writes its partial sum to slab s of C
 // ([k_splits][M][ldc]).  Whoever reads C adds the slabs in order (the norm and rotary kernels do), so the
@@ -66,8 +69,8 @@ __device__ __forceinline__ float epi_silu(float x) { return __fdividef(x, 1.0f +
 // epilogue and stores rows m0 + 32 * quarter + lane of C.
 template <int EPI, int W>
 __device__ __forceinline__ void drain_chunk(void* __restrict__ c, int ldc, int M, int n_cols, int split, int row, int col,
-                                            uint32_t t_chunk, uint32_t up_col) {
-    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU || EPI == EPI_GATED_RELU;
+                                            uint32_t t_chunk, uint32_t up_col, EpiParams ep) {
+    constexpr bool GATED = epi_gated(EPI);
     uint32_t v[W];
     float f[W];
     tc_ld<W>(t_chunk, v);
@@ -78,7 +81,12 @@ __device__ __forceinline__ void drain_chunk(void* __restrict__ c, int ldc, int M
 #pragma unroll
         for (int i = 0; i < W; ++i) {
             const float g = __uint_as_float(v[i]);
-            f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : EPI == EPI_GATED_SILU ? epi_silu(g) : fmaxf(g, 0.f)) * __uint_as_float(u[i]);
+            if (EPI == EPI_GATED_CAPPED) {       // g = min(gate, limit), u = clamp(up, -limit, limit): g sigmoid(slope g) (u + 1)
+                const float gc = fminf(g, ep.p0), uc = fminf(fmaxf(__uint_as_float(u[i]), -ep.p0), ep.p0);
+                f[i] = __fdividef(gc, 1.0f + __expf(-ep.p1 * gc)) * (uc + 1.0f);
+            } else {
+                f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : EPI == EPI_GATED_SILU ? epi_silu(g) : fmaxf(g, 0.f)) * __uint_as_float(u[i]);
+            }
         }
     } else {
         tc_wait_ld();
@@ -117,20 +125,20 @@ __device__ __forceinline__ void drain_chunk(void* __restrict__ c, int ldc, int M
 
 template <int EPI>
 __device__ __forceinline__ void drain_accumulator(void* __restrict__ c, int ldc, int M, int n_cols, int tile_n, int up_col,
-                                                  int split, int m0, int n0, uint32_t t_acc, int quarter, int lane) {
+                                                  int split, int m0, int n0, uint32_t t_acc, int quarter, int lane, EpiParams ep) {
     const int row = m0 + quarter * 32 + lane;
     const uint32_t t_row = t_acc + ((uint32_t)(quarter * 32) << 16);
     if (m0 + quarter * 32 >= M) return;                      // the same for the whole warp
     int c0 = 0;
 #pragma unroll 1
-    for (; c0 + 32 <= tile_n; c0 += 32) drain_chunk<EPI, 32>(c, ldc, M, n_cols, split, row, n0 + c0, t_row + c0, up_col);
-    if (c0 < tile_n) drain_chunk<EPI, 16>(c, ldc, M, n_cols, split, row, n0 + c0, t_row + c0, up_col);
+    for (; c0 + 32 <= tile_n; c0 += 32) drain_chunk<EPI, 32>(c, ldc, M, n_cols, split, row, n0 + c0, t_row + c0, up_col, ep);
+    if (c0 < tile_n) drain_chunk<EPI, 16>(c, ldc, M, n_cols, split, row, n0 + c0, t_row + c0, up_col, ep);
 }
 
 template <int EPI, int AROWS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
-               int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status) {
+               int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status, EpiParams ep) {
     constexpr int A_BYTES = Ring<AROWS>::A_BYTES, RING_BYTES = Ring<AROWS>::RING_BYTES, MAX_STAGES = Ring<AROWS>::MAX_STAGES;
     const int B_HALF = half_rows * BK * 2, STAGE_BYTES = A_BYTES + 2 * B_HALF;
     const int STAGES = min(MAX_STAGES, RING_BYTES / STAGE_BYTES);
@@ -144,7 +152,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU || EPI == EPI_GATED_RELU;
+    constexpr bool GATED = epi_gated(EPI);
     const int n_cols = GATED ? N / 2 : N;                       // columns of the output
     const int tile_n = GATED ? half_rows : 2 * half_rows;       // output columns per tile
     const int UP_COL = half_rows;                               // accumulator column where the second half begins
@@ -265,7 +273,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * tile_n;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
             tc_fence_after();
-            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, UP_COL, split, m0, n0, tmem_base + acc * BN, quarter, lane);
+            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, UP_COL, split, m0, n0, tmem_base + acc * BN, quarter, lane, ep);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);   // this warp has drained its quarter
@@ -311,7 +319,7 @@ struct PairRing {
 template <int EPI, bool WIDE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
-                    int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status) {
+                    int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status, EpiParams ep) {
     constexpr int A_BYTES = PairRing::A_BYTES, RING_BYTES = PairRing::RING_BYTES, MAX_STAGES = PairRing::MAX_STAGES;
     const int STAGE_BYTES = A_BYTES + half_rows * BK * 2;
     const int STAGES = min(MAX_STAGES, RING_BYTES / STAGE_BYTES);
@@ -326,7 +334,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU || EPI == EPI_GATED_RELU;
+    constexpr bool GATED = epi_gated(EPI);
     const int n_cols = GATED ? N / 2 : N;
     const int tile_n = GATED ? half_rows : 2 * half_rows;
     const int UP_COL = half_rows;
@@ -447,7 +455,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int m0 = (mn % tiles_m) * 2 * BM + (int)rank * BM, n0 = (mn / tiles_m) * tile_n;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
             tc_fence_after();
-            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, UP_COL, split, m0, n0, tmem_base + acc * BN, quarter, lane);
+            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, UP_COL, split, m0, n0, tmem_base + acc * BN, quarter, lane, ep);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -524,7 +532,7 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows,
 
 template <int EPI, int AROWS>
 static int launch_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                       int k_splits, int half_rows, int* status, int ctas, cudaStream_t stream) {
+                       int k_splits, int half_rows, int* status, int ctas, cudaStream_t stream, EpiParams ep = EpiParams{0.f, 0.f}) {
     // the tensor core reads 128 rows at a stage's A address whatever AROWS is: a stage must hold that many bytes
     if (Ring<AROWS>::A_BYTES + 2 * half_rows * BK * 2 < 128 * BK * 2) return WLLM_BAD_SIZE;
     static bool configured = false;
@@ -535,7 +543,7 @@ static int launch_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* c, in
         configured = true;
     }
     return wllm_launch(gemm_tc_kernel<EPI, AROWS>, ctas, NUM_THREADS, Ring<AROWS>::SMEM_BYTES, stream, ma, mw, c, ldc, M, N, K,
-                       up_off, k_splits, half_rows, status);
+                       up_off, k_splits, half_rows, status, ep);
 }
 
 // How many pairs can be resident at once.  The kernel is persistent with a fixed stride over the tiles, so
@@ -565,7 +573,7 @@ static int resident_pairs() {
 
 template <int EPI, bool WIDE>
 static int launch_pair_as(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                          int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream) {
+                          int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream, EpiParams ep = EpiParams{0.f, 0.f}) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -577,18 +585,18 @@ static int launch_pair_as(const CUtensorMap& ma, const CUtensorMap& mw, void* c,
     if (resident < 1) return WLLM_BAD_SIZE;
     if (pairs > resident) pairs = resident;
     return wllm_launch(gemm_tc_pair_kernel<EPI, WIDE>, 2 * pairs, NUM_THREADS, PairRing::SMEM_BYTES, stream, ma, mw, c, ldc, M, N,
-                       K, up_off, k_splits, half_rows, status);
+                       K, up_off, k_splits, half_rows, status, ep);
 }
 
 template <int EPI>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                       int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream) {
-    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU || EPI == EPI_GATED_RELU;
+                       int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream, EpiParams ep = EpiParams{0.f, 0.f}) {
+    constexpr bool GATED = epi_gated(EPI);
     if constexpr (!GATED) {
         if (half_rows > 128)
-            return launch_pair_as<EPI, true>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, pairs, stream);
+            return launch_pair_as<EPI, true>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, pairs, stream, ep);
     }
-    return launch_pair_as<EPI, false>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, pairs, stream);
+    return launch_pair_as<EPI, false>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, pairs, stream, ep);
 }
 
 // Number of CTA pairs of the two-CTA kernel that one device holds at once (for reports).
@@ -611,12 +619,12 @@ static int a_rows_for(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 
 template <int EPI>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                  int k_splits, int half_rows, int* status, int ctas, cudaStream_t stream) {
+                  int k_splits, int half_rows, int* status, int ctas, cudaStream_t stream, EpiParams ep = EpiParams{0.f, 0.f}) {
     switch (a_rows_for(M)) {
-        case 32: return launch_rows<EPI, 32>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream);
-        case 64: return launch_rows<EPI, 64>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream);
+        case 32: return launch_rows<EPI, 32>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream, ep);
+        case 64: return launch_rows<EPI, 64>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream, ep);
     }
-    return launch_rows<EPI, 128>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream);
+    return launch_rows<EPI, 128>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream, ep);
 }
 
 // C = A W^T.  epilogue 0: bf16 C [M, N]; 1: fp32 C [M, N]; 2 / 3: W = [gate; up] ([N, K], N even), bf16 C [M, N/2]
@@ -625,9 +633,13 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc
 // half_rows (a multiple of 16 up to 128; 0 = 128) sets the width of a tile: 2 * half_rows output columns, or
 // half_rows columns of the gated output (by 128 rows, or 256 rows on a pair of CTAs).  On pairs without a gate
 // it may also be a multiple of 8, or 144 to 256 in steps of 16 (wide tiles, see the pair kernel).
-WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
-                               int epilogue, int k_splits, int half_rows, int* status, int max_ctas, cudaStream_t stream) {
+// epilogue 5: the clamped gated unit g = min(gate, p0), u = clamp(up, -p0, p0), g sigmoid(p1 g) (u + 1), with its two constants.
+WLLM_API int wllm_gemm_bf16_tc_params(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
+                                      int epilogue, int k_splits, int half_rows, int* status, int max_ctas, float p0, float p1,
+                                      cudaStream_t stream) {
+    const EpiParams ep{p0, p1};
     if (M <= 0 || N <= 0) return WLLM_OK;
+    if (epilogue < 0 || epilogue > EPI_GATED_CAPPED) return WLLM_BAD_SIZE;
     if (k_splits < 1 || (k_splits > 1 && epilogue != EPI_F32)) return WLLM_BAD_SIZE;
     {
         const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
@@ -635,7 +647,7 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
     }
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K) return WLLM_BAD_SIZE;
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15)) return WLLM_BAD_ALIGN;
-    const bool gated = epilogue == EPI_GATED_GELU || epilogue == EPI_GATED_SILU || epilogue == EPI_GATED_RELU;
+    const bool gated = epi_gated(epilogue) && epilogue <= EPI_GATED_CAPPED;
     if (gated && (N % 2 != 0)) return WLLM_BAD_SIZE;
     const bool pair = M > BM && max_ctas >= 2 && pair_enabled();
     if (half_rows == 0) half_rows = 128;
@@ -660,6 +672,7 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
             case EPI_GATED_GELU: return launch_pair<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
             case EPI_GATED_SILU: return launch_pair<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
             case EPI_GATED_RELU: return launch_pair<EPI_GATED_RELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
+            case EPI_GATED_CAPPED: return launch_pair<EPI_GATED_CAPPED>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream, ep);
         }
         return WLLM_BAD_SIZE;
     }
@@ -671,6 +684,13 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
         case EPI_GATED_GELU: return launch<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
         case EPI_GATED_SILU: return launch<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
         case EPI_GATED_RELU: return launch<EPI_GATED_RELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
+        case EPI_GATED_CAPPED: return launch<EPI_GATED_CAPPED>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream, ep);
     }
     return WLLM_BAD_SIZE;
+}
+
+WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
+                               int epilogue, int k_splits, int half_rows, int* status, int max_ctas, cudaStream_t stream) {
+    if (epilogue == EPI_GATED_CAPPED) return WLLM_BAD_SIZE;      // needs its constants: wllm_gemm_bf16_tc_params
+    return wllm_gemm_bf16_tc_params(a, lda, w, ldw, c, ldc, M, N, K, epilogue, k_splits, half_rows, status, max_ctas, 0.f, 0.f, stream);
 }

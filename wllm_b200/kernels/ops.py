@@ -386,9 +386,10 @@ def decode_split_plan(heads: int, max_ctx: int, tile: int) -> tuple:
 
 def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, nq: int, nkv: int,
                          hd: int, page_size: int, window: int, scale: float, split_keys: int, max_splits: int,
-                         scratch: torch.Tensor, sinks: torch.Tensor | None = None) -> None:
+                         scratch: torch.Tensor, sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0) -> None:
     """bfloat16 attention of the requests that bring one token (csrc/attention_mma.cu, decode).
-    `sinks`: float32 [nq], one more term e^sink of every row's softmax denominator."""
+    `sinks`: float32 [nq], one more term e^sink of every row's softmax denominator.  `cap` > 0: scores become
+    cap * tanh(score / cap); `keep` > 0 (with a window): the sequence's first `keep` keys stay visible behind the window."""
     _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, scratch, sinks)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
@@ -396,13 +397,13 @@ def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_c
     R = req_q_len.shape[0]
     assert scratch.numel() >= attention_mma_scratch_floats(R, nq, hd, max_splits)
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
-    _check(lib.wllm_attention_mma_decode_sinks(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+    _check(lib.wllm_attention_mma_decode_capped(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
                                                ctypes.c_longlong(k_pages.shape[0]),
                                                _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
                                                _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                                _ptr(_int32(block_table, "block_table")), block_table.shape[1], R, nq, nkv,
                                                page_size, window, c_float(scale), split_keys, max_splits, _ptr(scratch),
-                                               _ptr(_status_word(q.device)), _ptr(sinks), _stream()),
+                                               _ptr(_status_word(q.device)), _ptr(sinks), c_float(cap), keep, _stream()),
            f"attention_mma_decode(head_dim={hd}, heads={nq}/{nkv})")
     global launches
     launches += 1 if max_splits > 1 else 0    # the merge kernel
@@ -441,10 +442,11 @@ def prefill_share_plan(q_lens, ctx_lens, nq: int, nkv: int, hd: int, skip_single
 def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, max_q_len: int,
                           nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
                           skip_single: bool, split_above: int = 0, halves: torch.Tensor | None = None,
-                          sinks: torch.Tensor | None = None) -> None:
+                          sinks: torch.Tensor | None = None, cap: float = 0.0, keep: int = 0) -> None:
     """bfloat16 attention of the requests that bring several tokens (csrc/attention_mma.cu, prefill).
     split_above > 0 (head sizes in steps of 64): a tile of 128 rows that walks more than that many tiles of 64
-    keys is computed by two CTAs, half of the keys each; `halves` (float32) holds their partial results."""
+    keys is computed by two CTAs, half of the keys each; `halves` (float32) holds their partial results.
+    `cap`, `keep`: as for attention_mma_decode; with either the mma.sync kernel that walks a list of key tiles runs."""
     _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, halves, sinks)
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous())
     if split_above > 0:
@@ -453,14 +455,14 @@ def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_
     assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
-    _check(lib.wllm_attention_mma_prefill_sinks(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+    _check(lib.wllm_attention_mma_prefill_capped(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
                                                 ctypes.c_longlong(k_pages.shape[0]),
                                                 _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
                                                 _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                                 _ptr(_int32(block_table, "block_table")), block_table.shape[1],
                                                 req_q_len.shape[0], max_q_len, nq, nkv, page_size, window, c_float(scale),
                                                 1 if skip_single else 0, split_above, _ptr(halves) if split_above > 0 else None,
-                                                _ptr(_status_word(q.device)), _ptr(sinks), _stream()),
+                                                _ptr(_status_word(q.device)), _ptr(sinks), c_float(cap), keep, _stream()),
            f"attention_mma_prefill(head_dim={hd}, heads={nq}/{nkv})")
 
 
@@ -532,7 +534,7 @@ def fma_peak_tflops(device, iters: int = 20000) -> float:
     return best
 
 
-_TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3, "relu": 4}
+_TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3, "relu": 4, "capped_swish": 5}
 _tc_status: dict = {}
 
 
@@ -619,9 +621,11 @@ def split_plan(M: int, N: int, K: int) -> int:
 
 
 def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "bf16",
-                 max_ctas: int | None = None, k_splits: int = 1, half_rows: int | None = None, checked: bool = False) -> torch.Tensor:
+                 max_ctas: int | None = None, k_splits: int = 1, half_rows: int | None = None, checked: bool = False,
+                 limit: float = 0.0, slope: float = 0.0) -> torch.Tensor:
     """out = a @ w^T on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu).  epilogue 'bf16' | 'f32' (32-bit out) |
-    'gelu_tanh' | 'silu' | 'relu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)).
+    'gelu_tanh' | 'silu' | 'relu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)) | 'capped_swish' (the
+    clamped gated unit of gated_act, with its `limit` and `slope`).
     k_splits > 1 ('f32' only) cuts K into parts; `out` is then [k_splits, M, N] partial sums.
     half_rows: the tile of products of at most 128 rows (see tile_plan, which chooses it when None)."""
     _need_cuda(a, w, out)
@@ -644,8 +648,8 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
     lib = load_family("gemm_bf16_tc")
     if half_rows is None:
         half_rows = tile_plan(M, N, K, code >= 2, k_splits > 1)[0]
-    _check(lib.wllm_gemm_bf16_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
-                                 k_splits, half_rows, _ptr(status), max_ctas, _stream()),
+    _check(lib.wllm_gemm_bf16_tc_params(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
+                                        k_splits, half_rows, _ptr(status), max_ctas, c_float(limit), c_float(slope), _stream()),
            f"gemm_bf16_tc({M}x{N}x{K}, {epilogue}, {k_splits} parts)")
     return out
 
@@ -713,8 +717,8 @@ def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.
     gated_act, with its `limit` and `slope`).  bfloat16 with enough rows: one
     tensor-memory GEMM whose epilogue applies the activation; otherwise product, then activation kernel
     (`scratch(shape, dtype)` supplies the [n, 2I] intermediate)."""
-    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_gate_up) and act in _TC_EPILOGUES:
-        return gemm_bf16_tc(a, w_gate_up, out, act, checked=True)
+    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_gate_up):
+        return gemm_bf16_tc(a, w_gate_up, out, act, checked=True, limit=limit, slope=slope)
     gu = linear(a, w_gate_up, scratch((a.shape[0], w_gate_up.shape[0]), a.dtype))
     return gated_act(gu, out, act, limit, slope)
 

@@ -63,7 +63,7 @@ class PagedAttention:
         self.sink_name = spec.options.get("sink")
         self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
         # the tensor-core kernels take keys and values of one size; other shapes run on the general kernels
-        self.general = self.vd != self.hd or self.softcap > 0 or self.keep_first > 0
+        self.general = self.vd != self.hd
         # columns of the fused q|k|v row (q alone in a mixer that reads another's keys and values)
         self.width = self.nq * self.hd if self.borrows else (self.nq + self.nkv) * self.hd + self.nkv * self.vd
         self.tag = ""                    # set by a mixer that runs this one beside another: keeps their buffers apart
@@ -101,8 +101,8 @@ class PagedAttention:
 
     def mix(self, fused: torch.Tensor, parts: int, col0: int, ctx, cache: CacheRef):
         """The mixer on columns col0 .. col0 + width of a fused product [n, W] (or partial sums [parts, n, W])."""
-        if self.borrows == cache.writes:
-            raise ValueError("an attention mixer without key and value projections reads another run's cache, and only such a one")
+        if self.borrows and cache.writes:
+            raise ValueError("an attention mixer without key and value projections must stand in a run that reads another run's cache")
         n = fused.shape[-2]
         qkv = fused if fused.shape[-1] == self.width else fused[..., col0:col0 + self.width]
         group = ctx.cache.groups[cache.group]
@@ -145,6 +145,9 @@ class PagedAttention:
             return
         decode = ctx.num_single > 0 and nq // nkv <= 16
         extra = {"sinks": self.sinks} if self.sinks is not None else {}
+        listed = self.softcap > 0 or self.keep_first > 0       # the kernels that walk a list of key tiles (mma.sync)
+        if listed:
+            extra.update(cap=self.softcap, keep=self.keep_first)
         if decode:
             R = ctx.n_requests
             # one CTA fits on an SM: every (request, kv head) is cut into parts so that the CTAs finish together
@@ -155,7 +158,7 @@ class PagedAttention:
             ops.attention_mma_decode(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
                                      nq, nkv, hd, ps, window, scale, split_keys, max_splits, scratch, **extra)
         if ctx.num_multi > 0 or not decode:
-            split_above, halves = self._shared_tiles(ctx, skip_single=decode)
+            split_above, halves = (0, None) if listed else self._shared_tiles(ctx, skip_single=decode)
             ops.attention_mma_prefill(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
                                       ctx.max_q_len, nq, nkv, hd, ps, window, scale, skip_single=decode,
                                       split_above=split_above, halves=halves, **extra)
