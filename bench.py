@@ -632,10 +632,9 @@ def taritar_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int)
                                                                                  hd ** -0.5, skip_single=False), T * nq * hd * 4, 4.0 * nq * hd * T * T / 2)
     row("prefill/gemma attention (window)", lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, window,
                                                                                hd ** -0.5, skip_single=False), T * nq * hd * 4, 4.0 * nq * hd * seen)
-    from wllm_b200.parts.attention import PagedAttention  # noqa: F401  (the kernels below are the ones the mixer picks)
     row("prefill/attention with cap, window and kept keys",
-        lambda: taritar_attention(ops, q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, window, hd ** -0.5, 30.0, keep, True),
-        T * nq * hd * 4, 4.0 * nq * hd * seen)
+        lambda: ops.attention_mma_prefill(q, ao, kp, vp, one * 0, one * T, one * T, table, T, nq, nkv, hd, ps, window, hd ** -0.5,
+                                          skip_single=False, cap=30.0, keep=keep), T * nq * hd * 4, 4.0 * nq * hd * seen)
     per = -(-(context + 1) // ps)
     dtable = torch.arange(batch * per, dtype=i32, device=dev).view(batch, per)
     qd, od = rnd(batch, nq * hd, dtype=bf), torch.empty(batch, nq * hd, dtype=bf, device=dev)
@@ -649,8 +648,8 @@ def taritar_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int)
     row("decode/gemma attention (window)", lambda: ops.attention_mma_decode(qd, od, kp, vp, starts, lens, ctxs, dtable, nq, nkv, hd, ps, window, hd ** -0.5,
                                                                              split_keys, max_splits, scratch), batch * read * nkv * hd * 2 * 2)
     row("decode/attention with cap, window and kept keys",
-        lambda: taritar_attention(ops, qd, od, kp, vp, starts, lens, ctxs, dtable, 1, nq, nkv, hd, ps, window, hd ** -0.5, 30.0, keep, False),
-        batch * read * nkv * hd * 2 * 2)
+        lambda: ops.attention_mma_decode(qd, od, kp, vp, starts, lens, ctxs, dtable, nq, nkv, hd, ps, window, hd ** -0.5, split_keys,
+                                         max_splits, scratch, cap=30.0, keep=keep), batch * read * nkv * hd * 2 * 2)
     # ---- feed-forward: Gemma's dense unit; the clamped unit; the router, the plan and the grouped products of the experts
     for n, tag in ((T, "prefill"), (batch, "decode")):
         x = rnd(n, W, dtype=bf)
@@ -694,13 +693,6 @@ def taritar_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int)
     logits = rnd(batch, size["vocab"])
     row("decode/tanh cap of the logits", lambda: ops.tanh_cap(logits, 30.0), batch * size["vocab"] * 8)
     return out
-
-
-def taritar_attention(ops, q, out, kp, vp, starts, lens, ctxs, table, max_q_len, nq, nkv, hd, ps, window, scale, cap, keep, multi):
-    """The launches that the attention mixer makes for a step of bfloat16 rows with a cap and kept keys (parts/attention.py)."""
-    import torch
-    from wllm_b200.parts.attention import capped_attention_launch
-    capped_attention_launch(ops, q, out, kp, vp, starts, lens, ctxs, table, max_q_len, nq, nkv, hd, ps, window, scale, cap, keep, multi)
 
 
 def taritar_bench(args) -> int:

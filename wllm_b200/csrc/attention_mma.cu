@@ -965,8 +965,11 @@ WLLM_API int wllm_attention_mma_decode_capped(const void* q, int q_stride, void*
         return WLLM_BAD_SIZE;
     CUtensorMap km, vm;
     const long long rows = pool_pages * nkv * page_size;
-    const int box_rows = USE_TMA ? (page_size < WS_BN ? page_size : WS_BN) : (page_size < BN ? page_size : BN);
-    const bool whole_rows = USE_TMA && box_rows == WS_BN;      // pages of at least a tile's keys: one copy a tile
+    // the warp-specialised kernel copies tiles of WS_BN keys (one three-dimensional box a tile where a page holds one);
+    // the kernel that walks a list of tiles copies two-dimensional boxes of up to BN keys, as the prefill kernel does
+    const bool ws = USE_TMA && !listed;
+    const int box_rows = ws ? (page_size < WS_BN ? page_size : WS_BN) : (page_size < BN ? page_size : BN);
+    const bool whole_rows = ws && box_rows == WS_BN;      // pages of at least a tile's keys: one copy a tile
     int r = pool_map(k_pages, rows, box_rows, &km, whole_rows);
     if (r) return r;
     r = pool_map(v_pages, rows, box_rows, &vm, whole_rows);

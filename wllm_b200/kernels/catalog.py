@@ -13,6 +13,8 @@ FAMILIES = {
     "attention_simt": [{}],
     "activation": [{}],
     "linear_attention": [{}],
+    "hyper_connections": [{}],
+    "moe": [{}],
     "gemm_f32": [{}],
     "sampling": [{}],
     "staging": [{}],
