@@ -438,3 +438,37 @@ def test_the_clamped_unit_in_the_products_epilogue(M):
     want = gate * torch.sigmoid(slope * gate) * (up + 1)
     assert (out.cpu().double() - want).abs().max() < 0.02 and float((a.double() @ w.double()[:I].T > limit).float().mean()) > 0.1
     assert ops.tc_gemm_status(DEV) == 0
+
+
+@pytest.mark.parametrize("hd,rot", [(48, 48), (128, 64), (32, 16)])
+def test_interleaved_rotation_of_many_rows_is_that_of_few(hd, rot):
+    """A prompt of many bfloat16 rows takes a kernel of its own (a CTA a token, 16-byte loads); its bits are those of the
+    kernel that serves few rows, and both match the plain rotation of the pairs (2i, 2i + 1)."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(hd)
+    n, nq, nkv, ps = 300, 3, 2, 16
+    qkv = torch.randn(n, (nq + 2 * nkv) * hd, generator=g).bfloat16()
+    pos = torch.randint(0, 5000, (n,), generator=g).to(torch.int32)
+    slots = torch.randperm(20 * ps, generator=g)[:n].to(torch.int32)
+    inv = (500.0 ** (-torch.arange(0, rot, 2, dtype=torch.float64) / rot)).float()
+    outs = []
+    for pieces in (1, 3):
+        q = torch.zeros(n, nq * hd, dtype=torch.bfloat16, device=DEV)
+        kp, vp = (torch.zeros(20, nkv, ps, hd, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+        step = n // pieces
+        for i in range(0, n, step):
+            ops.rope_kv_write(qkv[i:i + step].to(DEV), q[i:i + step], pos[i:i + step].to(DEV), slots[i:i + step].to(DEV), inv.to(DEV),
+                              kp, vp, nq, nkv, hd, rot, ps, pairing="interleaved")
+        outs.append((q.cpu(), kp.cpu(), vp.cpu()))
+    assert all(torch.equal(a, b) for a, b in zip(*outs))
+    want = plain.rotate_interleaved(qkv[:, :nq * hd].double().view(n, nq, hd), pos.long(), rot, 500.0).reshape(n, -1)
+    assert (outs[0][0].double() - want).abs().max() < 0.03
+    krow = outs[0][1][slots[7] // ps, 1, slots[7] % ps].double()
+    kwant = plain.rotate_interleaved(qkv[7:8, (nq + 1) * hd:(nq + 2) * hd].double().view(1, 1, hd), pos[7:8].long(), rot, 500.0).reshape(-1)
+    assert (krow - kwant).abs().max() < 0.03
+    assert torch.equal(outs[0][2][slots[7] // ps, 0, slots[7] % ps], qkv[7, (nq + nkv) * hd:(nq + nkv + 1) * hd])
+    # queries alone, as a layer rotates them that reads another layer's keys and values
+    q2 = torch.zeros(n, nq * hd, dtype=torch.bfloat16, device=DEV)
+    ops.rope_kv_write(qkv[:, :nq * hd].contiguous().to(DEV), q2, pos.to(DEV), None, inv.to(DEV), None, None, nq, 0, hd, rot, ps,
+                      pairing="interleaved")
+    assert torch.equal(q2.cpu(), outs[0][0])

@@ -21,7 +21,7 @@
 constexpr int MOE_MAX_EXPERTS = 1024;
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(1024)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ w_gate,
                  int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ gate_out, int H, int E, int top,
                  int groups, int groups_kept) {
@@ -35,9 +35,19 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
     __syncthreads();
     for (int e = warp; e < E + (w_gate != nullptr ? 1 : 0); e += nwarps) {
         const float* w = e < E ? w_router + (size_t)e * H : w_gate;
-        float acc = 0.f;
-        for (int c = lane; c < H; c += 32) acc = fmaf(w[c], hs[c], acc);
-        acc = warp_sum(acc);
+        // a lane's share of the row as four chains (elements c, c+1, c+2, c+3 of every 128), added in a fixed order:
+        // the sum depends on the row and H alone
+        float a4[4] = {0.f, 0.f, 0.f, 0.f};
+        if ((H & 3) == 0) {
+            for (int c = lane * 4; c < H; c += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + c);
+                a4[0] = fmaf(wv.x, hs[c], a4[0]); a4[1] = fmaf(wv.y, hs[c + 1], a4[1]);
+                a4[2] = fmaf(wv.z, hs[c + 2], a4[2]); a4[3] = fmaf(wv.w, hs[c + 3], a4[3]);
+            }
+        } else {
+            for (int c = lane; c < H; c += 32) a4[0] = fmaf(w[c], hs[c], a4[0]);
+        }
+        float acc = warp_sum((a4[0] + a4[1]) + (a4[2] + a4[3]));
         if (lane == 0) {
             if (e < E) sc[e] = acc; else gate_out[t] = 1.0f / (1.0f + expf(-acc));
         }
@@ -94,9 +104,12 @@ __global__ void __launch_bounds__(128) moe_count_kernel(const int* __restrict__ 
     const int e = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (e >= E) return;
     int c = 0;
-    for (int p0 = 0; p0 < pairs; p0 += 32) {
-        const int p = p0 + lane;
-        c += __popc(__ballot_sync(0xffffffffu, p < pairs && chosen[p] == e));
+    for (int p0 = 0; p0 < pairs; p0 += 128) {          // four loads in flight a lane
+        bool mine[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { const int p = p0 + 32 * u + lane; mine[u] = p < pairs && chosen[p] == e; }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) c += __popc(__ballot_sync(0xffffffffu, mine[u]));
     }
     if (lane == 0) count[e] = c;
 }
@@ -116,16 +129,20 @@ __global__ void __launch_bounds__(128) moe_place_kernel(const int* __restrict__ 
         if (e == E - 1) offset[E] = before + count[e];
     }
     int at = before;
-    for (int p0 = 0; p0 < pairs; p0 += 32) {
-        const int p = p0 + lane;
-        const bool mine = p < pairs && chosen[p] == e;
-        const unsigned b = __ballot_sync(0xffffffffu, mine);
-        if (mine) {
-            const int r = at + __popc(b & ((1u << lane) - 1u));
-            sorted[r] = p;
-            place[p] = r;
+    for (int p0 = 0; p0 < pairs; p0 += 128) {          // four loads in flight a lane; the pairs still go in ascending order
+        bool mine[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { const int p = p0 + 32 * u + lane; mine[u] = p < pairs && chosen[p] == e; }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const unsigned b = __ballot_sync(0xffffffffu, mine[u]);
+            if (mine[u]) {
+                const int r = at + __popc(b & ((1u << lane) - 1u));
+                sorted[r] = p0 + 32 * u + lane;
+                place[p0 + 32 * u + lane] = r;
+            }
+            at += __popc(b);
         }
-        at += __popc(b);
     }
 }
 
@@ -218,6 +235,153 @@ moe_grouped_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ 
     }
 }
 
+// The same products for bfloat16 operands on the tensor cores (mma.sync m16n8k16, 32-bit accumulators): a CTA of eight
+// warps takes 64 rows of one expert by 128 rows of W (128 output columns, or, gated, 64 gate rows and the 64 up rows of
+// the same columns, laid out so that a thread holds gate and up of the same output element), K in blocks of 32 through
+// a ring of three cp.async stages; rows of A are gathered through `sorted` while they are copied.  K in steps of 8.
+constexpr int TM = 64, TN = 128, TK = 32, TPITCH = TK + 8, TSTAGES = 3;      // a pitch of 80 bytes: ldmatrix without bank conflicts
+
+__device__ __forceinline__ void moe_cp16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void moe_ldsm4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void moe_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The tile's expert and rows from the offsets, by one warp: tiles are dealt expert by expert, ceil(count / rows_per_tile) each.
+__device__ __forceinline__ void moe_find_tile(const int* __restrict__ offset, int E, int rows_per_tile, int tile, int lane,
+                                              int& expert, int& row0, int& rows) {
+    expert = -1; row0 = 0; rows = 0;
+    int base = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+        const int e = e0 + lane;
+        const int lo = e < E ? offset[e] : 0, cnt = e < E ? offset[e + 1] - lo : 0;
+        const int tiles = (cnt + rows_per_tile - 1) / rows_per_tile;
+        int incl = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+        const int first = base + incl - tiles;
+        const bool mine = tile >= first && tile < base + incl;
+        const unsigned b = __ballot_sync(0xffffffffu, mine);
+        if (b) {
+            const int src = __ffs(b) - 1;
+            const int k = tile - __shfl_sync(0xffffffffu, first, src);
+            expert = e0 + src;
+            row0 = __shfl_sync(0xffffffffu, lo, src) + k * rows_per_tile;
+            rows = min(rows_per_tile, __shfl_sync(0xffffffffu, cnt, src) - k * rows_per_tile);
+            return;
+        }
+        base += __shfl_sync(0xffffffffu, incl, 31);
+    }
+}
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w, TO* __restrict__ out, int N, int K,
+                       const int* __restrict__ offset, const int* __restrict__ sorted, int E, int top, float limit, float slope) {
+    __shared__ __align__(16) bf16 As[TSTAGES][TM][TPITCH];
+    __shared__ __align__(16) bf16 Ws[TSTAGES][TN][TPITCH];
+    __shared__ int s_tile[3];
+    pdl_begin();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 0) {
+        int e, r0, rs;
+        moe_find_tile(offset, E, TM, blockIdx.y, lane, e, r0, rs);
+        if (lane == 0) { s_tile[0] = e; s_tile[1] = r0; s_tile[2] = rs; }
+    }
+    __syncthreads();
+    const int e = s_tile[0];
+    if (e < 0) return;
+    const int row0 = s_tile[1], rows = s_tile[2];
+    constexpr int COLS = GATED ? TN / 2 : TN;               // output columns of a tile
+    const int col0 = blockIdx.x * COLS;
+    const bf16* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+    // what this thread copies a stage: one 16-byte piece of A (64 rows x 4 pieces) and two of W (128 rows x 4 pieces)
+    const int a_row = threadIdx.x >> 2, piece = threadIdx.x & 3;
+    const bf16* a_src = nullptr;
+    if (a_row < rows) a_src = a + (size_t)(GATED ? sorted[row0 + a_row] / top : row0 + a_row) * a_stride;
+    const bf16* w_src[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int r = a_row + 64 * u;                       // row of the W tile
+        int col;
+        if (GATED) { const int wn = r >> 5, rr = r & 31; col = ((rr >> 4) ? N : 0) + col0 + 16 * wn + (rr & 15); if (col0 + 16 * wn + (rr & 15) >= N) col = -1; }
+        else { col = col0 + r; if (col >= N) col = -1; }
+        w_src[u] = col >= 0 ? we + (size_t)col * K : nullptr;
+    }
+    auto load = [&](int kb, int stage) {
+        const int k = kb * TK + piece * 8;
+        const bool in_k = k < K;
+        moe_cp16((uint32_t)__cvta_generic_to_shared(&As[stage][a_row][piece * 8]), a_src ? a_src + k : a, a_src != nullptr && in_k);
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+            moe_cp16((uint32_t)__cvta_generic_to_shared(&Ws[stage][a_row + 64 * u][piece * 8]), w_src[u] ? w_src[u] + k : w, w_src[u] != nullptr && in_k);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int wm = warp & 1, wn = warp >> 1;                // 2 x 4 warps: 32 rows by 32 rows of W each
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    const int kblocks = (K + TK - 1) / TK;
+    for (int s0 = 0; s0 < TSTAGES - 1; ++s0) {
+        if (s0 < kblocks) load(s0, s0); else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kb = 0; kb < kblocks; ++kb) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(TSTAGES - 2) : "memory");
+        __syncthreads();                                    // block kb is here for everyone; the stage of block kb-1 is free
+        if (kb + TSTAGES - 1 < kblocks) load(kb + TSTAGES - 1, (kb + TSTAGES - 1) % TSTAGES);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        const int st = kb % TSTAGES;
+#pragma unroll
+        for (int kk = 0; kk < TK / 16; ++kk) {
+            uint32_t af[2][4], bfr[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+                moe_ldsm4((uint32_t)__cvta_generic_to_shared(&As[st][wm * 32 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][kk * 16 + (lane >> 4) * 8]), af[mi]);
+#pragma unroll
+            for (int nj = 0; nj < 2; ++nj)
+                moe_ldsm4((uint32_t)__cvta_generic_to_shared(&Ws[st][wn * 32 + nj * 16 + (lane & 7) + (lane >> 4) * 8][kk * 16 + ((lane >> 3) & 1) * 8]), bfr[nj]);
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+                for (int nj = 0; nj < 2; ++nj) {
+                    moe_mma(acc[mi][2 * nj], af[mi], bfr[nj][0], bfr[nj][1]);
+                    moe_mma(acc[mi][2 * nj + 1], af[mi], bfr[nj][2], bfr[nj][3]);
+                }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm * 32 + mi * 16 + (lane >> 2) + half * 8;
+            if (r >= rows) continue;
+            TO* orow = out + (size_t)(row0 + r) * N;
+#pragma unroll
+            for (int ni = 0; ni < (GATED ? 2 : 4); ++ni)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int col = GATED ? col0 + 16 * wn + 8 * ni + (lane & 3) * 2 + c : col0 + wn * 32 + ni * 8 + (lane & 3) * 2 + c;
+                    if (col >= N) continue;
+                    float v = acc[mi][ni][half * 2 + c];
+                    if (GATED) {
+                        const float g = fminf(v, limit), u = fminf(fmaxf(acc[mi][ni + 2][half * 2 + c], -limit), limit);
+                        v = (g / (1.0f + expf(-slope * g))) * (u + 1.0f);
+                    }
+                    orow[col] = from_f32<TO>(v);
+                }
+        }
+}
+
 // out[t][c] = sum_k weights[t][k] * y[place[t top + k]][c]  (+ gate[t] * shared[t][c], shared a tensor of TS or `parts`
 // 32-bit partial sums added in order first)
 template <typename TS>
@@ -253,12 +417,13 @@ WLLM_API int wllm_moe_route(const void* h, int dtype, const float* w_router, con
         return WLLM_BAD_SIZE;
     const size_t smem = (size_t)(H + E + groups) * sizeof(float);
     if (smem > 200 * 1024) return WLLM_BAD_SIZE;
+    const int threads = 32 * (E + 1 < 4 ? 4 : (E + 1 > 32 ? 32 : E + 1));      // a warp an expert (and the shared gate), up to 32
 #define GO(T) do { \
         if (smem > 48 * 1024) { \
             const cudaError_t er = cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
             if (er != cudaSuccess) return 1000 + (int)er; \
         } \
-        return wllm_launch(moe_route_kernel<T>, n, 128, smem, stream, (const T*)h, w_router, w_gate, chosen, weights, gate_out, H, E, \
+        return wllm_launch(moe_route_kernel<T>, n, threads, smem, stream, (const T*)h, w_router, w_gate, chosen, weights, gate_out, H, E, \
                            top, groups, groups_kept); \
     } while (0)
     if (dtype == WLLM_BF16) GO(bf16);
@@ -286,6 +451,15 @@ WLLM_API int wllm_moe_grouped(const void* a, int a_stride, const void* w, void* 
     if (grid.y > 65535) return WLLM_BAD_SIZE;
 #define GO(T, TO, G) wllm_launch(moe_grouped_kernel<T, TO, G>, grid, 256, 0, stream, (const T*)a, a_stride, (const T*)w, (TO*)out, N, K, \
                                  offset, sorted, E, top, limit, slope)
+    if (dtype == WLLM_BF16 && K % 8 == 0 && a_stride % 8 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
+        const dim3 tgrid((N + (gated ? TN / 2 : TN) - 1) / (gated ? TN / 2 : TN), (pairs + TM - 1) / TM + E);
+        if (tgrid.y > 65535) return WLLM_BAD_SIZE;
+        if (gated)
+            return wllm_launch(moe_grouped_mma_kernel<bf16, true>, tgrid, 256, 0, stream, (const bf16*)a, a_stride, (const bf16*)w,
+                               (bf16*)out, N, K, offset, sorted, E, top, limit, slope);
+        return wllm_launch(moe_grouped_mma_kernel<float, false>, tgrid, 256, 0, stream, (const bf16*)a, a_stride, (const bf16*)w,
+                           (float*)out, N, K, offset, sorted, E, top, limit, slope);
+    }
     if (dtype == WLLM_BF16) return gated ? GO(bf16, bf16, true) : GO(bf16, float, false);
     if (dtype == WLLM_F32) return gated ? GO(float, float, true) : GO(float, float, false);
 #undef GO

@@ -259,7 +259,8 @@ rope_unit_norm_rows_kernel(const bf16* __restrict__ qkv, int row_stride, bf16* _
 __global__ void rope_kv_write_rows_kernel(const bf16* __restrict__ qkv, int row_stride, bf16* __restrict__ q_out, int q_stride,
                                           const int* __restrict__ positions, const int* __restrict__ slots,
                                           const float* __restrict__ inv_freq, bf16* __restrict__ k_pages,
-                                          bf16* __restrict__ v_pages, int nq, int nkv, int hd, int rot_dim, int page_size) {
+                                          bf16* __restrict__ v_pages, int nq, int nkv, int hd, int rot_dim, int page_size,
+                                          int interleaved) {
     extern __shared__ float sc[];            // [half] sines, [half] cosines
     pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -282,6 +283,28 @@ __global__ void rope_kv_write_rows_kernel(const bf16* __restrict__ qkv, int row_
     for (int item = threadIdx.x; item < rotated * per_head; item += blockDim.x) {
         const int h = item / per_head, j = (item % per_head) * 8;
         const bf16* x = row + (size_t)h * hd;
+        if (interleaved) {          // the pairs (2j, 2j+1) .. (2j+14, 2j+15): sixteen neighbouring elements
+            const uint4 a = *reinterpret_cast<const uint4*>(x + 2 * j), b = *reinterpret_cast<const uint4*>(x + 2 * j + 8);
+            const bf16* xa = reinterpret_cast<const bf16*>(&a);
+            const bf16* xb = reinterpret_cast<const bf16*>(&b);
+            uint4 ya, yb;
+            bf16* pa = reinterpret_cast<bf16*>(&ya);
+            bf16* pb = reinterpret_cast<bf16*>(&yb);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const bf16* src = e < 4 ? xa : xb;
+                bf16* to = e < 4 ? pa : pb;
+                const int o = (e & 3) * 2;
+                float y1, y2;
+                rotate_pair(to_f32(src[o]), to_f32(src[o + 1]), sc[j + e], sc[half + j + e], y1, y2);
+                to[o] = from_f32<bf16>(y1);
+                to[o + 1] = from_f32<bf16>(y2);
+            }
+            bf16* dst = dst_of(h);
+            *reinterpret_cast<uint4*>(dst + 2 * j) = ya;
+            *reinterpret_cast<uint4*>(dst + 2 * j + 8) = yb;
+            continue;
+        }
         const uint4 a = *reinterpret_cast<const uint4*>(x + j), b = *reinterpret_cast<const uint4*>(x + j + half);
         const bf16* xa = reinterpret_cast<const bf16*>(&a);
         const bf16* xb = reinterpret_cast<const bf16*>(&b);
@@ -320,12 +343,12 @@ WLLM_API int wllm_rope_kv_write_general(const void* qkv, int in_dtype, int row_s
     if (n <= 0) return WLLM_OK;
     if (hd <= 0 || vd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv < 0 || (nkv == 0 && slots != nullptr) || in_splits < 1)
         return WLLM_BAD_SIZE;
-    if (n >= 256 && !interleaved && vd == hd && !unit_norm && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && rot_dim % 16 == 0 &&
+    if (n >= 256 && vd == hd && !unit_norm && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && rot_dim % 16 == 0 &&
         row_stride % 8 == 0 && q_stride % 8 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) &&
         !((uintptr_t)k_pages & 15) && !((uintptr_t)v_pages & 15))
         return wllm_launch(rope_kv_write_rows_kernel, n, 128, (size_t)rot_dim * sizeof(float), stream, (const bf16*)qkv, row_stride,
                            (bf16*)q_out, q_stride, positions, slots, inv_freq, (bf16*)k_pages, (bf16*)v_pages, nq, nkv, hd,
-                           rot_dim, page_size);
+                           rot_dim, page_size, interleaved);
     if (unit_norm) {
         if (hd > 512) return WLLM_BAD_SIZE;
         if (n >= 256 && !interleaved && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && vd % 8 == 0 &&
