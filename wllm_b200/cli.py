@@ -20,7 +20,7 @@ import time
 
 
 def parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="wllm_b200", description="LLM inference on one B200 (Gemma 1, Pesanex)")
+    ap = argparse.ArgumentParser(prog="wllm_b200", description="LLM inference on one B200 (Gemma 1, Pesanex, Taritar)")
     ap.add_argument("--model", help="folder with config.json and model.safetensors")
     ap.add_argument("--device", default="cuda", choices=["cuda"], help="the engine has no CPU path")
     ap.add_argument("--num-blocks", type=int, default=256, help="KV cache blocks (block_size tokens each)")

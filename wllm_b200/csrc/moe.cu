@@ -20,40 +20,60 @@
 
 constexpr int MOE_MAX_EXPERTS = 1024;
 
+// A CTA takes `tpb` tokens: a warp an expert (and one for the shared gate) reads its row of the router once and runs it
+// against the CTA's tokens; then a warp a token does the softmax and the choice.
 template <typename T>
 __global__ void __launch_bounds__(1024)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, const float* __restrict__ w_gate,
-                 int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ gate_out, int H, int E, int top,
-                 int groups, int groups_kept) {
-    extern __shared__ float route_smem[];          // [H] the token's row, [E] scores, [groups] group scores
-    float* hs = route_smem;
-    float* sc = hs + H;
-    float* gs = sc + E;
+                 int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ gate_out, int n, int H, int E, int top,
+                 int groups, int groups_kept, int tpb) {
+    extern __shared__ float route_smem[];          // [tpb][H] the tokens' rows, [tpb][E] scores, [tpb][groups] group scores
+    float* hs_all = route_smem;
+    float* sc_all = hs_all + (size_t)tpb * H;
+    float* gs_all = sc_all + (size_t)tpb * E;
     pdl_begin();
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) hs[c] = to_f32(h[(size_t)t * H + c]);
+    const int t0 = blockIdx.x * tpb, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int here = min(tpb, n - t0);
+    for (int i = threadIdx.x; i < here * H; i += blockDim.x) hs_all[i] = to_f32(h[(size_t)t0 * H + i]);
     __syncthreads();
+    constexpr int TB = 4;                          // tokens a pass over the router's row
     for (int e = warp; e < E + (w_gate != nullptr ? 1 : 0); e += nwarps) {
         const float* w = e < E ? w_router + (size_t)e * H : w_gate;
-        // a lane's share of the row as four chains (elements c, c+1, c+2, c+3 of every 128), added in a fixed order:
-        // the sum depends on the row and H alone
-        float a4[4] = {0.f, 0.f, 0.f, 0.f};
-        if ((H & 3) == 0) {
-            for (int c = lane * 4; c < H; c += 128) {
-                const float4 wv = *reinterpret_cast<const float4*>(w + c);
-                a4[0] = fmaf(wv.x, hs[c], a4[0]); a4[1] = fmaf(wv.y, hs[c + 1], a4[1]);
-                a4[2] = fmaf(wv.z, hs[c + 2], a4[2]); a4[3] = fmaf(wv.w, hs[c + 3], a4[3]);
+        for (int j0 = 0; j0 < here; j0 += TB) {
+            // a lane's share of a row as four chains (elements c .. c+3 of every 128), added in a fixed order: the sum
+            // depends on the token's row and H alone, not on the tokens beside it
+            float a4[TB][4];
+#pragma unroll
+            for (int j = 0; j < TB; ++j) a4[j][0] = a4[j][1] = a4[j][2] = a4[j][3] = 0.f;
+            if ((H & 3) == 0) {
+                for (int c = lane * 4; c < H; c += 128) {
+                    const float4 wv = *reinterpret_cast<const float4*>(w + c);
+#pragma unroll
+                    for (int j = 0; j < TB; ++j) {
+                        const float* hs = hs_all + (size_t)min(j0 + j, here - 1) * H;
+                        a4[j][0] = fmaf(wv.x, hs[c], a4[j][0]); a4[j][1] = fmaf(wv.y, hs[c + 1], a4[j][1]);
+                        a4[j][2] = fmaf(wv.z, hs[c + 2], a4[j][2]); a4[j][3] = fmaf(wv.w, hs[c + 3], a4[j][3]);
+                    }
+                }
+            } else {
+                for (int c = lane; c < H; c += 32)
+#pragma unroll
+                    for (int j = 0; j < TB; ++j) a4[j][0] = fmaf(w[c], hs_all[(size_t)min(j0 + j, here - 1) * H + c], a4[j][0]);
             }
-        } else {
-            for (int c = lane; c < H; c += 32) a4[0] = fmaf(w[c], hs[c], a4[0]);
-        }
-        float acc = warp_sum((a4[0] + a4[1]) + (a4[2] + a4[3]));
-        if (lane == 0) {
-            if (e < E) sc[e] = acc; else gate_out[t] = 1.0f / (1.0f + expf(-acc));
+#pragma unroll
+            for (int j = 0; j < TB; ++j) {
+                const float acc = warp_sum((a4[j][0] + a4[j][1]) + (a4[j][2] + a4[j][3]));
+                if (lane == 0 && j0 + j < here) {
+                    if (e < E) sc_all[(size_t)(j0 + j) * E + e] = acc; else gate_out[t0 + j0 + j] = 1.0f / (1.0f + expf(-acc));
+                }
+            }
         }
     }
     __syncthreads();
-    if (warp == 0) {
+    for (int j = warp; j < here; j += nwarps) {
+        const int t = t0 + j;
+        float* sc = sc_all + (size_t)j * E;
+        float* gs = gs_all + (size_t)j * groups;
         float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
         m = warp_max(m);
@@ -66,7 +86,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
         const int per = E / groups;
         for (int g = lane; g < groups; g += 32) {
             float best = -INFINITY;
-            for (int j = 0; j < per; ++j) best = fmaxf(best, sc[g * per + j]);
+            for (int i = 0; i < per; ++i) best = fmaxf(best, sc[g * per + i]);
             gs[g] = best;
         }
         __syncwarp();
@@ -237,9 +257,10 @@ moe_grouped_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ 
 
 // The same products for bfloat16 operands on the tensor cores (mma.sync m16n8k16, 32-bit accumulators): a CTA of eight
 // warps takes 64 rows of one expert by 128 rows of W (128 output columns, or, gated, 64 gate rows and the 64 up rows of
-// the same columns, laid out so that a thread holds gate and up of the same output element), K in blocks of 32 through
+// the same columns, laid out so that a thread holds gate and up of the same output element), K in blocks of 64 through
 // a ring of three cp.async stages; rows of A are gathered through `sorted` while they are copied.  K in steps of 8.
-constexpr int TM = 64, TN = 128, TK = 32, TPITCH = TK + 8, TSTAGES = 3;      // a pitch of 80 bytes: ldmatrix without bank conflicts
+constexpr int TM = 64, TN = 128, TK = 64, TPITCH = TK + 8, TSTAGES = 3;      // a pitch of 144 bytes: ldmatrix without bank conflicts
+constexpr int T_SMEM = TSTAGES * (TM + TN) * TPITCH * 2;
 
 __device__ __forceinline__ void moe_cp16(uint32_t dst, const void* src, bool valid) {
     const int n = valid ? 16 : 0;
@@ -285,8 +306,9 @@ template <typename TO, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w, TO* __restrict__ out, int N, int K,
                        const int* __restrict__ offset, const int* __restrict__ sorted, int E, int top, float limit, float slope) {
-    __shared__ __align__(16) bf16 As[TSTAGES][TM][TPITCH];
-    __shared__ __align__(16) bf16 Ws[TSTAGES][TN][TPITCH];
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    bf16 (*As)[TM][TPITCH] = reinterpret_cast<bf16 (*)[TM][TPITCH]>(moe_smem);
+    bf16 (*Ws)[TN][TPITCH] = reinterpret_cast<bf16 (*)[TN][TPITCH]>(moe_smem + TSTAGES * TM * TPITCH * 2);
     __shared__ int s_tile[3];
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -302,8 +324,8 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
     constexpr int COLS = GATED ? TN / 2 : TN;               // output columns of a tile
     const int col0 = blockIdx.x * COLS;
     const bf16* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
-    // what this thread copies a stage: one 16-byte piece of A (64 rows x 4 pieces) and two of W (128 rows x 4 pieces)
-    const int a_row = threadIdx.x >> 2, piece = threadIdx.x & 3;
+    // what this thread copies a stage: two 16-byte pieces of a row of A (64 rows x 8 pieces) and of two rows of W (128 rows)
+    const int a_row = threadIdx.x >> 2, piece0 = threadIdx.x & 3;
     const bf16* a_src = nullptr;
     if (a_row < rows) a_src = a + (size_t)(GATED ? sorted[row0 + a_row] / top : row0 + a_row) * a_stride;
     const bf16* w_src[2];
@@ -316,12 +338,16 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
         w_src[u] = col >= 0 ? we + (size_t)col * K : nullptr;
     }
     auto load = [&](int kb, int stage) {
-        const int k = kb * TK + piece * 8;
-        const bool in_k = k < K;
-        moe_cp16((uint32_t)__cvta_generic_to_shared(&As[stage][a_row][piece * 8]), a_src ? a_src + k : a, a_src != nullptr && in_k);
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
-            moe_cp16((uint32_t)__cvta_generic_to_shared(&Ws[stage][a_row + 64 * u][piece * 8]), w_src[u] ? w_src[u] + k : w, w_src[u] != nullptr && in_k);
+        for (int pc = 0; pc < TK / 32; ++pc) {
+            const int piece = piece0 + 4 * pc, k = kb * TK + piece * 8;
+            const bool in_k = k < K;
+            moe_cp16((uint32_t)__cvta_generic_to_shared(&As[stage][a_row][piece * 8]), a_src ? a_src + k : a, a_src != nullptr && in_k);
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                moe_cp16((uint32_t)__cvta_generic_to_shared(&Ws[stage][a_row + 64 * u][piece * 8]), w_src[u] ? w_src[u] + k : w,
+                         w_src[u] != nullptr && in_k);
+        }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const int wm = warp & 1, wn = warp >> 1;                // 2 x 4 warps: 32 rows by 32 rows of W each
@@ -415,7 +441,11 @@ WLLM_API int wllm_moe_route(const void* h, int dtype, const float* w_router, con
     if (H <= 0 || E <= 0 || E > MOE_MAX_EXPERTS || top < 1 || groups < 1 || E % groups != 0 || groups_kept < 1 ||
         groups_kept > groups || top > groups_kept * (E / groups) || (w_gate != nullptr && gate_out == nullptr))
         return WLLM_BAD_SIZE;
-    const size_t smem = (size_t)(H + E + groups) * sizeof(float);
+    // tokens a CTA: eight once the tokens alone fill the device (each row of the router is then read once for eight), as
+    // long as their rows fit in shared memory
+    int tpb = n >= 1024 ? 8 : (n >= 296 ? 2 : 1);
+    while (tpb > 1 && (size_t)tpb * (H + E + groups) * sizeof(float) > 160 * 1024) tpb >>= 1;
+    const size_t smem = (size_t)tpb * (H + E + groups) * sizeof(float);
     if (smem > 200 * 1024) return WLLM_BAD_SIZE;
     const int threads = 32 * (E + 1 < 4 ? 4 : (E + 1 > 32 ? 32 : E + 1));      // a warp an expert (and the shared gate), up to 32
 #define GO(T) do { \
@@ -423,8 +453,8 @@ WLLM_API int wllm_moe_route(const void* h, int dtype, const float* w_router, con
             const cudaError_t er = cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
             if (er != cudaSuccess) return 1000 + (int)er; \
         } \
-        return wllm_launch(moe_route_kernel<T>, n, threads, smem, stream, (const T*)h, w_router, w_gate, chosen, weights, gate_out, H, E, \
-                           top, groups, groups_kept); \
+        return wllm_launch(moe_route_kernel<T>, (n + tpb - 1) / tpb, threads, smem, stream, (const T*)h, w_router, w_gate, chosen, weights, \
+                           gate_out, n, H, E, top, groups, groups_kept, tpb); \
     } while (0)
     if (dtype == WLLM_BF16) GO(bf16);
     if (dtype == WLLM_F32) GO(float);
@@ -454,10 +484,17 @@ WLLM_API int wllm_moe_grouped(const void* a, int a_stride, const void* w, void* 
     if (dtype == WLLM_BF16 && K % 8 == 0 && a_stride % 8 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)w & 15)) {
         const dim3 tgrid((N + (gated ? TN / 2 : TN) - 1) / (gated ? TN / 2 : TN), (pairs + TM - 1) / TM + E);
         if (tgrid.y > 65535) return WLLM_BAD_SIZE;
+        static bool raised = false;
+        if (!raised) {
+            cudaError_t er = cudaFuncSetAttribute(moe_grouped_mma_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
+            if (er == cudaSuccess) er = cudaFuncSetAttribute(moe_grouped_mma_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM);
+            if (er != cudaSuccess) return 1000 + (int)er;
+            raised = true;
+        }
         if (gated)
-            return wllm_launch(moe_grouped_mma_kernel<bf16, true>, tgrid, 256, 0, stream, (const bf16*)a, a_stride, (const bf16*)w,
+            return wllm_launch(moe_grouped_mma_kernel<bf16, true>, tgrid, 256, T_SMEM, stream, (const bf16*)a, a_stride, (const bf16*)w,
                                (bf16*)out, N, K, offset, sorted, E, top, limit, slope);
-        return wllm_launch(moe_grouped_mma_kernel<float, false>, tgrid, 256, 0, stream, (const bf16*)a, a_stride, (const bf16*)w,
+        return wllm_launch(moe_grouped_mma_kernel<float, false>, tgrid, 256, T_SMEM, stream, (const bf16*)a, a_stride, (const bf16*)w,
                            (float*)out, N, K, offset, sorted, E, top, limit, slope);
     }
     if (dtype == WLLM_BF16) return gated ? GO(bf16, bf16, true) : GO(bf16, float, false);
