@@ -46,13 +46,17 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
 #pragma unroll
             for (int j = 0; j < TB; ++j) a4[j][0] = a4[j][1] = a4[j][2] = a4[j][3] = 0.f;
             if ((H & 3) == 0) {
-                for (int c = lane * 4; c < H; c += 128) {
+                const float* hrow[TB];
+#pragma unroll
+                for (int j = 0; j < TB; ++j) hrow[j] = hs_all + (size_t)min(j0 + j, here - 1) * H;
+#pragma unroll 4
+                for (int c = lane * 4; c < H; c += 128) {           // several of the router's 16-byte loads in flight
                     const float4 wv = *reinterpret_cast<const float4*>(w + c);
 #pragma unroll
                     for (int j = 0; j < TB; ++j) {
-                        const float* hs = hs_all + (size_t)min(j0 + j, here - 1) * H;
-                        a4[j][0] = fmaf(wv.x, hs[c], a4[j][0]); a4[j][1] = fmaf(wv.y, hs[c + 1], a4[j][1]);
-                        a4[j][2] = fmaf(wv.z, hs[c + 2], a4[j][2]); a4[j][3] = fmaf(wv.w, hs[c + 3], a4[j][3]);
+                        const float4 hv = *reinterpret_cast<const float4*>(hrow[j] + c);
+                        a4[j][0] = fmaf(wv.x, hv.x, a4[j][0]); a4[j][1] = fmaf(wv.y, hv.y, a4[j][1]);
+                        a4[j][2] = fmaf(wv.z, hv.z, a4[j][2]); a4[j][3] = fmaf(wv.w, hv.w, a4[j][3]);
                     }
                 }
             } else {
@@ -257,9 +261,10 @@ moe_grouped_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ 
 
 // The same products for bfloat16 operands on the tensor cores (mma.sync m16n8k16, 32-bit accumulators): a CTA of eight
 // warps takes 64 rows of one expert by 128 rows of W (128 output columns, or, gated, 64 gate rows and the 64 up rows of
-// the same columns, laid out so that a thread holds gate and up of the same output element), K in blocks of 64 through
+// the same columns, laid out so that a thread holds gate and up of the same output element), K in blocks of 32 through
 // a ring of three cp.async stages; rows of A are gathered through `sorted` while they are copied.  K in steps of 8.
-constexpr int TM = 64, TN = 128, TK = 64, TPITCH = TK + 8, TSTAGES = 3;      // a pitch of 144 bytes: ldmatrix without bank conflicts
+constexpr int TM = 64, TN = 128, TK = 32, TPITCH = TK + 8, TSTAGES = 3;      // a pitch of 80 bytes: ldmatrix without bank conflicts
+// (blocks of 64 of K were measured too: 83 KB a CTA leave two CTAs an SM instead of four, 334 -> 362 us at 8,192 rows)
 constexpr int T_SMEM = TSTAGES * (TM + TN) * TPITCH * 2;
 
 __device__ __forceinline__ void moe_cp16(uint32_t dst, const void* src, bool valid) {
@@ -324,7 +329,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
     constexpr int COLS = GATED ? TN / 2 : TN;               // output columns of a tile
     const int col0 = blockIdx.x * COLS;
     const bf16* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
-    // what this thread copies a stage: two 16-byte pieces of a row of A (64 rows x 8 pieces) and of two rows of W (128 rows)
+    // what this thread copies a stage: TK / 32 16-byte pieces of a row of A (64 rows) and of two rows of W (128 rows)
     const int a_row = threadIdx.x >> 2, piece0 = threadIdx.x & 3;
     const bf16* a_src = nullptr;
     if (a_row < rows) a_src = a + (size_t)(GATED ? sorted[row0 + a_row] / top : row0 + a_row) * a_stride;
