@@ -5,8 +5,10 @@
          feed-forward that reads an earlier layer's keys and values under a wider mask of its own, and a layer that sees
          every key, has no cap and no rotation, and routes to one expert without groups or a shared one
 'one'    a single stream (all connection tensors of size one); windows no longer than a page, kept keys equal to the
-         window and beyond it, one key/value head
-'plain'  no streams at all (a plain residual), no logit cap, one expert group kept of one
+         window and beyond it, one key/value head, heads of 28 elements (held as 32 with zeros behind them)
+'odd'    sizes in no step of 4 or 8 (width 50, heads of 10 and 6, feed-forwards of 30, 14 and 10, nine experts), five streams,
+         a layer with fewer query heads than the layer whose keys and values it reads
+'plain'  no streams at all (a plain residual), no logit cap, one expert group kept of one, heads of 12 and 20 elements
 """
 from __future__ import annotations
 
@@ -61,8 +63,8 @@ ONE = {
     "architecture": "Taritar", "vocab": 90, "width": 40, "max_positions": 300, "streams": 1, "logit_softcap": 30.0,
     "embedding": {"scale": 0.25}, "norm": {"eps": 1e-6},
     "layers": [
-        {"type": "attention", "mixer": _att(2, 1, 24, None, (24, 10000.0), None, 8.0, (16, 16)), "mlp": {"kind": "dense", "ff": 56, "limit": 3.0}},
-        {"type": "attention", "mixer": _att(2, 1, 24, None, (24, 10000.0), 0.5, None, (8, 33), kv_from=0),
+        {"type": "attention", "mixer": _att(2, 1, 28, None, (28, 10000.0), None, 8.0, (16, 16)), "mlp": {"kind": "dense", "ff": 56, "limit": 3.0}},
+        {"type": "attention", "mixer": _att(2, 1, 28, None, (28, 10000.0), 0.5, None, (8, 33), kv_from=0),
          "mlp": _moe(6, 3, 8, 0.7, groups=(2, 1), shared=(8, 1.0))},
         {"type": "attention", "mixer": _att(1, 1, 8, 16, (2, 50.0), None, 2.0, (13, 1)), "mlp": {"kind": "dense", "ff": 24, "limit": 1.5}},
     ],
@@ -72,13 +74,22 @@ PLAIN = {
     "architecture": "Taritar", "vocab": 64, "width": 48, "max_positions": 256,
     "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
     "layers": [
-        {"type": "attention", "mixer": _att(3, 3, 16, None, (16, 100.0), None, 10.0, (20, 3)), "mlp": _moe(4, 2, 16, 1.0, groups=(1, 1))},
-        {"type": "attention", "mixer": _att(3, 3, 16, None, (16, 100.0), None, 10.0, (64, 0), kv_from=0), "mlp": {"kind": "dense", "ff": 32, "limit": 1.0}},
+        {"type": "attention", "mixer": _att(3, 3, 12, 20, (6, 100.0), None, 10.0, (20, 3)), "mlp": _moe(4, 2, 16, 1.0, groups=(1, 1))},
+        {"type": "attention", "mixer": _att(3, 3, 12, 20, (6, 100.0), None, 10.0, (64, 0), kv_from=0), "mlp": {"kind": "dense", "ff": 32, "limit": 1.0}},
     ],
 }
 
-CONFIGS = {"wide": WIDE, "one": ONE, "plain": PLAIN}
-SEEDS = {"wide": 21, "one": 22, "plain": 23}
+ODD = {
+    "architecture": "Taritar", "vocab": 77, "width": 50, "max_positions": 260, "streams": 5, "logit_softcap": 4.0,
+    "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "attention", "mixer": _att(6, 2, 10, 6, (4, 30.0), 0.35, 7.0, (33, 2)), "mlp": _moe(9, 3, 10, 1.1, groups=(3, 2), shared=(14, 0.6))},
+        {"type": "attention", "mixer": _att(2, 2, 10, 6, (4, 30.0), 0.35, 7.0, (50, 31), kv_from=0), "mlp": {"kind": "dense", "ff": 30, "limit": 0.9}},
+    ],
+}
+
+CONFIGS = {"wide": WIDE, "one": ONE, "plain": PLAIN, "odd": ODD}
+SEEDS = {"wide": 21, "one": 22, "plain": 23, "odd": 24}
 
 
 def write_folder(folder: str, name: str, dtype=torch.bfloat16) -> str:

@@ -56,10 +56,15 @@ class PagedAttention:
             raise ValueError("softcap and keep_first must not be negative")
         self.position = POSITIONS.build(spec.position)
         self.vd = int(spec.options.get("value_dim") or self.hd)
-        if self.vd % 8 or self.hd % 8:
-            raise ValueError(f"head sizes {self.hd} / {self.vd}: the attention kernels read heads in steps of 8 elements")
         scale = spec.options.get("scale")
         self.scale = float(self.hd) ** -0.5 if scale is None else float(scale)
+        # The kernels read heads in steps of 8 elements.  A head of another size is held with zeros behind it, in the
+        # projections' rows (so that the products leave zeros there), in the pages and in the output projection's columns:
+        # zeros add nothing to a score or to an output.  `hd_file` / `vd_file` are the checkpoint's sizes.
+        self.hd_file, self.vd_file = self.hd, self.vd
+        self.hd, self.vd = -(-self.hd // 8) * 8, -(-self.vd // 8) * 8
+        if spec.options.get("qk_unit_norm_eps") is not None and self.hd != self.hd_file:
+            raise ValueError(f"head size {self.hd_file}: heads that are divided by their root mean square come in steps of 8 elements")
         self.sink_name = spec.options.get("sink")
         self.unit_norm_eps = spec.options.get("qk_unit_norm_eps")
         # the tensor-core kernels take keys and values of one size; other shapes run on the general kernels
@@ -74,20 +79,29 @@ class PagedAttention:
 
     def param_specs(self):
         H, n = self.hidden_size, self.names
-        out = [ParamSpec(n["q_proj"], (self.nq * self.hd, H)), ParamSpec(n["o_proj"], (H, self.nq * self.vd))]
+        out = [ParamSpec(n["q_proj"], (self.nq * self.hd_file, H)), ParamSpec(n["o_proj"], (H, self.nq * self.vd_file))]
         if not self.borrows:
-            out[1:1] = [ParamSpec(n["k_proj"], (self.nkv * self.hd, H)), ParamSpec(n["v_proj"], (self.nkv * self.vd, H))]
+            out[1:1] = [ParamSpec(n["k_proj"], (self.nkv * self.hd_file, H)), ParamSpec(n["v_proj"], (self.nkv * self.vd_file, H))]
         if self.sink_name is not None:
             out.append(ParamSpec(self.sink_name, (self.nq,), "vector"))
         return out
 
     def load(self, fetch):
         n = self.names
+        def heads_padded(w, heads, size, to):      # [heads * size, H] -> [heads * to, H] with zero rows behind every head
+            if size == to:
+                return w
+            out = w.new_zeros((heads, to, w.shape[1]))
+            out[:, :size] = w.view(heads, size, w.shape[1])
+            return out.view(heads * to, w.shape[1])
+        wq = heads_padded(fetch(n["q_proj"]), self.nq, self.hd_file, self.hd)
         if self.borrows:
-            self.wqkv = fetch(n["q_proj"]).contiguous()
+            self.wqkv = wq.contiguous()
         else:
-            self.wqkv = torch.cat([fetch(n["q_proj"]), fetch(n["k_proj"]), fetch(n["v_proj"])], dim=0).contiguous()
-        self.wo = fetch(n["o_proj"]).contiguous()
+            self.wqkv = torch.cat([wq, heads_padded(fetch(n["k_proj"]), self.nkv, self.hd_file, self.hd),
+                                   heads_padded(fetch(n["v_proj"]), self.nkv, self.vd_file, self.vd)], dim=0).contiguous()
+        wo = fetch(n["o_proj"])
+        self.wo = heads_padded(wo.t().contiguous(), self.nq, self.vd_file, self.vd).t().contiguous()
         if self.sink_name is not None:
             self.sinks = fetch(self.sink_name).to(torch.float32).contiguous()
         self.position.to(self.wo.device)
