@@ -472,3 +472,60 @@ def test_interleaved_rotation_of_many_rows_is_that_of_few(hd, rot):
     ops.rope_kv_write(qkv[:, :nq * hd].contiguous().to(DEV), q2, pos.to(DEV), None, inv.to(DEV), None, None, nq, 0, hd, rot, ps,
                       pairing="interleaved")
     assert torch.equal(q2.cpu(), outs[0][0])
+
+
+@pytest.mark.parametrize("n,E,top,H,I", [(300, 6, 4, 72, 24), (700, 5, 2, 64, 104), (130, 40, 8, 128, 264)])
+def test_experts_on_the_tensor_memory_product(n, E, top, H, I):
+    """Many rows: the tokens' rows copied into sorted order, row tiles of 128 rows of one expert each from the table that the
+    plan leaves on the device (experts with no row, with a few and with more than a tile), both products on tcgen05."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(n + E)
+    dtype = torch.bfloat16
+    x = torch.randn(n, H, generator=g).to(dtype)
+    w = {f"e{j}.{k}": (torch.randn(s, generator=g) * 0.2).to(dtype).double()
+         for j in range(E) for k, s in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))}
+    usable = E - 1                      # the last expert gets no row
+    chosen = torch.stack([torch.randperm(usable, generator=g)[:top] for _ in range(n)]).to(torch.int32)
+    chosen[: n // 2, 0] = 0             # one expert with more than a tile of rows
+    for t in range(n // 2):             # (no expert twice for a token)
+        for k in range(1, top):
+            if chosen[t, k] == 0:
+                chosen[t, k] = usable - 1 if (usable - 1) not in chosen[t].tolist() else [e for e in range(usable) if e not in chosen[t].tolist()][0]
+    weights = torch.rand(n, top, generator=g)
+    limit, slope = 0.9, 1.702
+    want = torch.zeros(n, H, dtype=torch.float64)
+    for t in range(n):
+        for k in range(top):
+            want[t] += weights[t, k].double() * plain.capped_glu(w, f"e{int(chosen[t, k])}.", x[t:t + 1].double(), limit)[0]
+    w_gu = torch.stack([torch.cat([w[f"e{j}.gate"], w[f"e{j}.up"]]) for j in range(E)]).to(dtype).to(DEV)
+    w_d = torch.stack([w[f"e{j}.down"] for j in range(E)]).to(dtype).to(DEV)
+    pairs = n * top
+    count, offset = torch.empty(E, dtype=torch.int32, device=DEV), torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    order, place = torch.empty(pairs, dtype=torch.int32, device=DEV), torch.empty(pairs, dtype=torch.int32, device=DEV)
+    tiles = torch.full((1 + 3 * ops.moe_row_tiles(pairs, E),), -7, dtype=torch.int32, device=DEV)
+    ops.moe_plan(chosen.to(DEV), count, offset, order, place, tiles)
+    table = tiles.cpu().tolist()
+    counts = torch.bincount(chosen.reshape(-1).long(), minlength=E).tolist()
+    assert table[0] == sum(-(-c // 128) for c in counts) and counts[-1] == 0 and (max(counts) > 128) == (n >= 300)
+    seen = []
+    for i in range(table[0]):
+        e, row0, rows = table[1 + 3 * i: 4 + 3 * i]
+        seen.extend(range(row0, row0 + rows))
+        assert 0 < rows <= 128 and int(offset[e]) <= row0 and row0 + rows <= int(offset[e + 1])
+    assert seen == list(range(pairs))
+    rows = ops.moe_gather(x.to(DEV), order, top, torch.empty(pairs, H, dtype=dtype, device=DEV))
+    assert torch.equal(rows.cpu(), x[(order.cpu().long() // top)])
+    act = ops.gemm_bf16_tc_grouped(rows, w_gu, torch.empty(pairs, I, dtype=dtype, device=DEV), tiles, True, limit, slope)
+    y = ops.gemm_bf16_tc_grouped(act, w_d, torch.empty(pairs, H, device=DEV), tiles, False)
+    out = ops.moe_combine(y, place, weights.to(DEV), None, None, torch.empty(n, H, device=DEV))
+    assert ops.tc_gemm_status(DEV) == 0
+    assert (out.cpu().double() - want).abs().max() < 0.03 * max(1.0, float(want.abs().max()))
+
+
+def test_a_model_whose_experts_run_on_the_tensor_memory_product(setups, monkeypatch):
+    from wllm_b200.parts.experts import RoutedExperts
+    monkeypatch.setattr(RoutedExperts, "TC_FROM_PAIRS", 64)
+    folder, reqs, ref = setups["wide"]
+    steps = traces.whole(reqs)
+    runner = runner_for(folder, torch.bfloat16, 16, -(-traces.peak_tokens(steps) // 16))
+    close_enough(traces.run_in_process(runner, steps), ref, torch.bfloat16, "whole, experts on tcgen05")

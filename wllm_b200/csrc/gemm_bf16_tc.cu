@@ -289,6 +289,143 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------
+// Grouped: the rows of A are sorted by expert and every expert has a W of its own (w_rows rows each, one under the
+// other).  A row tile is 128 rows of ONE expert, from a table that a kernel before this one left on the device:
+// tiles[0] = number of row tiles, then (expert, first row, rows) a tile.  The tile's A box may reach into the next
+// expert's rows and its W box into the next expert's matrix: what they produce is not stored (rows from the expert's
+// last on, columns from N on).  One CTA a tile, as above, without parts of K and without loads ahead of the wait (the
+// table is the predecessor's).
+// ------------------------------------------------------------------------------------------------
+template <int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
+               int ldc, int N, int K, int w_rows, int up_row_offset, int half_rows, const int* __restrict__ tiles, int* __restrict__ status,
+                       EpiParams ep) {
+    constexpr int AROWS = 128;
+    constexpr int A_BYTES = Ring<AROWS>::A_BYTES, RING_BYTES = Ring<AROWS>::RING_BYTES, MAX_STAGES = Ring<AROWS>::MAX_STAGES;
+    const int B_HALF = half_rows * BK * 2, STAGE_BYTES = A_BYTES + 2 * B_HALF;
+    const int STAGES = min(MAX_STAGES, RING_BYTES / STAGE_BYTES);
+    extern __shared__ unsigned char smem_raw[];
+    // ring at a 1024-byte boundary (swizzle atoms), barriers behind it
+    const uint32_t ring = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = ring + RING_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + 8 * MAX_STAGES, tfull0 = bars + 16 * MAX_STAGES, tempty0 = tfull0 + 16;
+    const uint32_t tmem_slot = tempty0 + 16;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_addr(smem_raw)));
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr bool GATED = epi_gated(EPI);
+    const int n_cols = N;                                       // columns of the output (W holds 2 N rows an expert when gated)
+    const int tile_n = GATED ? half_rows : 2 * half_rows;       // output columns per tile
+    const int UP_COL = half_rows;                               // accumulator column where the second half begins
+    const uint32_t idesc = umma_idesc(BM, 2 * half_rows, false, false);
+    const int tiles_n = (n_cols + tile_n - 1) / tile_n;
+    const int kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            auto load_w = [&](uint32_t dst, uint32_t bar, int x, int y) { tma_load_2d(dst, &map_w, bar, x, y); };
+            pdl_wait();                    // the table of row tiles is the predecessor's work: nothing is asked for before it is there
+            const int tiles_m = tiles[0], num_tiles = tiles_m * tiles_n;
+            int issued = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int mt = tile % tiles_m, n0 = (tile / tiles_m) * tile_n;
+                const int expert = tiles[1 + 3 * mt], m0 = tiles[2 + 3 * mt];
+                const int w0 = expert * w_rows + n0;               // first row of the expert's W tile
+                for (int kb = 0; kb < kblocks; ++kb, ++issued) {
+                    const uint32_t a_dst = ring + stage * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * stage;
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) { ok = false; break; }
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
+                    load_w(b_dst, bar, kb * BK, w0);
+                    load_w(b_dst + B_HALF, bar, kb * BK, GATED ? up_row_offset + w0 : w0 + half_rows);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) atomicExch(status, GAVE_UP_PRODUCER);
+            // Loads still in flight land in this CTA's shared memory: stay until every stage that was
+            // filled has been consumed (its `empty` phase completes), or the limit passes.
+            for (int s = 0; s < STAGES; ++s) {
+                if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) break;
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            pdl_wait();
+            const int num_tiles = tiles[0] * tiles_n;
+            const int kb_lo = 0, kb_hi = kblocks;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kb = kb_lo; kb < kb_hi; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_src = ring + stage * STAGE_BYTES, b_src = a_src + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), idesc,
+                               (kb > kb_lo || k > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * stage);          // the stage is free once these products are done
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(tfull0 + 8 * acc);        // the accumulator is complete
+            }
+            if (!ok) atomicExch(status, GAVE_UP_MMA);
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, each its own quarter of the 128 lanes ----------------
+        pdl_wait();                  // C may still be read by the kernel before this one
+        const int quarter = warp & 3;
+        uint32_t it = 0;
+        bool ok = true;
+        const int tiles_m = tiles[0], num_tiles = tiles_m * tiles_n;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            const int mt = tile % tiles_m, n0 = (tile / tiles_m) * tile_n;
+            const int m0 = tiles[2 + 3 * mt], m_end = m0 + tiles[3 + 3 * mt];      // rows of the tile's expert only are stored
+            if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
+            tc_fence_after();
+            drain_accumulator<EPI>(c, ldc, m_end, n_cols, tile_n, UP_COL, 0, m0, n0, tmem_base + acc * BN, quarter, lane, ep);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * acc);   // this warp has drained its quarter
+        }
+        if (!ok && lane == 0) atomicExch(status, GAVE_UP_EPILOGUE);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Two CTAs per tile.  A cluster of two CTAs (on neighbouring SMs) shares a 256 x 256 tile: each holds its
 // own 128 rows of A and ONE half of the W tile (128 of the 256 rows), and tcgen05.mma.cta_group::2, issued
 // by the first CTA for both, multiplies each CTA's A rows by both halves.  A stage is then 32 KB instead
@@ -693,4 +830,46 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
                                int epilogue, int k_splits, int half_rows, int* status, int max_ctas, cudaStream_t stream) {
     if (epilogue == EPI_GATED_CAPPED) return WLLM_BAD_SIZE;      // needs its constants: wllm_gemm_bf16_tc_params
     return wllm_gemm_bf16_tc_params(a, lda, w, ldw, c, ldc, M, N, K, epilogue, k_splits, half_rows, status, max_ctas, 0.f, 0.f, stream);
+}
+
+template <int EPI>
+static int launch_grouped(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int N, int K, int w_rows, int up_off,
+                          int half_rows, const int* tiles, int* status, int ctas, cudaStream_t stream, EpiParams ep) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_grouped_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring<128>::SMEM_BYTES);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        configured = true;
+    }
+    return wllm_launch(gemm_tc_grouped_kernel<EPI>, ctas, NUM_THREADS, Ring<128>::SMEM_BYTES, stream, ma, mw, c, ldc, N, K, w_rows, up_off,
+                       half_rows, tiles, status, ep);
+}
+
+// The experts' products: a [rows, K] bf16 rows sorted by expert, w [experts * w_rows, K] (w_rows = N, or 2 N = [gate; up] with the
+// gated epilogue 5), c [rows, N] (32-bit with epilogue 1, bf16 with 0 and 5), tiles: the table of row tiles on the device (at most
+// max_row_tiles of them).  K in steps of 8.
+WLLM_API int wllm_gemm_bf16_tc_grouped(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int rows, int N, int K,
+                                       int experts, int epilogue, const int* tiles, int max_row_tiles, int* status, int max_ctas,
+                                       float p0, float p1, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return WLLM_OK;
+    if (epilogue != EPI_BF16 && epilogue != EPI_F32 && epilogue != EPI_GATED_CAPPED) return WLLM_BAD_SIZE;
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K || experts < 1 || max_row_tiles < 1) return WLLM_BAD_SIZE;
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15) || tiles == nullptr) return WLLM_BAD_ALIGN;
+    const bool gated = epilogue == EPI_GATED_CAPPED;
+    const int w_rows = gated ? 2 * N : N, half_rows = 128;
+    CUtensorMap ma, mw;
+    int r = tensor_map(a, rows, K, lda, 128, &ma);
+    if (r) return r;
+    r = tensor_map(w, experts * w_rows, K, ldw, half_rows, &mw);
+    if (r) return r;
+    const int tile_n = gated ? half_rows : 2 * half_rows;
+    const long long most = (long long)max_row_tiles * ((N + tile_n - 1) / tile_n);
+    const int ctas = (int)(most < max_ctas ? most : max_ctas);
+    const EpiParams ep{p0, p1};
+    switch (epilogue) {
+        case EPI_BF16: return launch_grouped<EPI_BF16>(ma, mw, c, ldc, N, K, w_rows, 0, half_rows, tiles, status, ctas, stream, ep);
+        case EPI_F32: return launch_grouped<EPI_F32>(ma, mw, c, ldc, N, K, w_rows, 0, half_rows, tiles, status, ctas, stream, ep);
+        case EPI_GATED_CAPPED: return launch_grouped<EPI_GATED_CAPPED>(ma, mw, c, ldc, N, K, w_rows, N, half_rows, tiles, status, ctas, stream, ep);
+    }
+    return WLLM_BAD_SIZE;
 }

@@ -140,17 +140,35 @@ __global__ void __launch_bounds__(128) moe_count_kernel(const int* __restrict__ 
 
 // offset[e] = count[0] + .. + count[e-1] (offset[E] = pairs); the pairs of expert e in ascending order fill the sorted
 // rows from offset[e]: sorted[r] = pair, place[pair] = r.
+// With `tiles` (null: none): the table of row tiles of `tile_rows` rows of one expert each, for the products that walk it:
+// tiles[0] = their number, then (expert, first sorted row, rows) a tile, expert by expert.
 __global__ void __launch_bounds__(128) moe_place_kernel(const int* __restrict__ chosen, int pairs, int E, const int* __restrict__ count,
-                                                        int* __restrict__ offset, int* __restrict__ sorted, int* __restrict__ place) {
+                                                        int* __restrict__ offset, int* __restrict__ sorted, int* __restrict__ place,
+                                                        int* __restrict__ tiles, int tile_rows) {
     pdl_begin();
     const int e = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (e >= E) return;
-    int before = 0;
-    for (int j = lane; j < e; j += 32) before += count[j];
-    for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+    int before = 0, tiles_before = 0;
+    for (int j = lane; j < e; j += 32) {
+        const int c = count[j];
+        before += c;
+        if (tiles) tiles_before += (c + tile_rows - 1) / tile_rows;
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        before += __shfl_xor_sync(0xffffffffu, before, o);
+        tiles_before += __shfl_xor_sync(0xffffffffu, tiles_before, o);
+    }
     if (lane == 0) {
         offset[e] = before;
         if (e == E - 1) offset[E] = before + count[e];
+    }
+    if (tiles) {
+        const int mine = count[e], n_tiles = (mine + tile_rows - 1) / tile_rows;
+        for (int t = lane; t < n_tiles; t += 32) {
+            int* entry = tiles + 1 + 3 * (tiles_before + t);
+            entry[0] = e; entry[1] = before + t * tile_rows; entry[2] = min(tile_rows, mine - t * tile_rows);
+        }
+        if (e == E - 1 && lane == 0) tiles[0] = tiles_before + n_tiles;
     }
     int at = before;
     for (int p0 = 0; p0 < pairs; p0 += 128) {          // four loads in flight a lane; the pairs still go in ascending order
@@ -468,12 +486,36 @@ WLLM_API int wllm_moe_route(const void* h, int dtype, const float* w_router, con
 }
 
 // count [E], offset [E + 1], sorted [pairs], place [pairs]
-WLLM_API int wllm_moe_plan(const int* chosen, int pairs, int E, int* count, int* offset, int* sorted, int* place, cudaStream_t stream) {
+// tiles (null: none): 1 + 3 * (ceil(pairs / tile_rows) + E) ints, the table of row tiles (see moe_place_kernel)
+WLLM_API int wllm_moe_plan_tiles(const int* chosen, int pairs, int E, int* count, int* offset, int* sorted, int* place, int* tiles,
+                                 int tile_rows, cudaStream_t stream) {
     if (pairs <= 0) return WLLM_OK;
-    if (E <= 0 || E > MOE_MAX_EXPERTS) return WLLM_BAD_SIZE;
+    if (E <= 0 || E > MOE_MAX_EXPERTS || (tiles != nullptr && tile_rows < 1)) return WLLM_BAD_SIZE;
     const int st = wllm_launch(moe_count_kernel, (E + 3) / 4, 128, 0, stream, chosen, pairs, E, count);
     if (st != WLLM_OK) return st;
-    return wllm_launch(moe_place_kernel, (E + 3) / 4, 128, 0, stream, chosen, pairs, E, (const int*)count, offset, sorted, place);
+    return wllm_launch(moe_place_kernel, (E + 3) / 4, 128, 0, stream, chosen, pairs, E, (const int*)count, offset, sorted, place, tiles,
+                       tile_rows);
+}
+
+WLLM_API int wllm_moe_plan(const int* chosen, int pairs, int E, int* count, int* offset, int* sorted, int* place, cudaStream_t stream) {
+    return wllm_moe_plan_tiles(chosen, pairs, E, count, offset, sorted, place, nullptr, 0, stream);
+}
+
+// out[r] = x[sorted[r] / top]: the tokens' rows in the order of the sorted pairs (K elements of 2 bytes, K in steps of 8)
+__global__ void __launch_bounds__(128) moe_gather_kernel(const bf16* __restrict__ x, int x_stride, const int* __restrict__ sorted, int top,
+                                                         bf16* __restrict__ out, int K) {
+    pdl_begin();
+    const int r = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(sorted[r] / top) * x_stride);
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * K);
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+WLLM_API int wllm_moe_gather(const void* x, int x_stride, const int* sorted, int top, void* out, int pairs, int K, cudaStream_t stream) {
+    if (pairs <= 0) return WLLM_OK;
+    if (K <= 0 || K % 8 != 0 || x_stride % 8 != 0 || top < 1) return WLLM_BAD_SIZE;
+    if (((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return WLLM_BAD_ALIGN;
+    return wllm_launch(moe_gather_kernel, pairs, 128, 0, stream, (const bf16*)x, x_stride, sorted, top, (bf16*)out, K);
 }
 
 // gated = 1: a [n][K] rows of tokens (stride a_stride), w [E][2 N][K], out [pairs][N] of the operands' type;

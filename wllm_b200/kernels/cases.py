@@ -9,6 +9,7 @@ print what it achieved against the roofline.  The same command under `ncu` gives
     python -m wllm_b200.kernels.cases gemm-f32 --m 16 --n 49152 --k 3072
     python -m wllm_b200.kernels.cases attention-f32 --requests 16 --context 6000 --tokens 1 --heads 16 --kv-heads 16
     python -m wllm_b200.kernels.cases recurrence --requests 1 --tokens 2048 --heads 8 --dim 128 --vdim 256
+    python -m wllm_b200.kernels.cases experts --tokens 2048 --experts 32 --top 4 --width 2048 --ff 1024
 
 Operands are larger than L2 where the case is bound by memory (several weight copies are cycled), so the
 figures are DRAM figures.  Peaks: MEASURED_PEAKS.json at the repository root when present, else the fallback
@@ -234,6 +235,52 @@ def recurrence(args) -> None:
           f"{fma / ms / 1e9:.2f} T 32-bit multiply-adds and multiplies a second")
 
 
+def experts(args) -> None:
+    """Routed experts at a layer's shape: router, the pairs sorted by expert, the two grouped products, the weighted sum."""
+    n, E, top, W, I = args.tokens, args.experts, args.top, args.width, args.ff
+    bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
+    x = (torch.randn(n, W, device=DEV)).to(bf)
+    wr, wg = torch.randn(E, W, device=DEV) * 0.05, torch.randn(W, device=DEV) * 0.05
+    copies = max(1, min(4, int(300e6 // (E * 3 * I * W * 2)) + 1))       # cycle the experts' weights so that they come from DRAM
+    w_gu = [(torch.randn(E, 2 * I, W, device=DEV) * 0.02).to(bf) for _ in range(copies)]
+    w_d = [(torch.randn(E, W, I, device=DEV) * 0.02).to(bf) for _ in range(copies)]
+    pairs = n * top
+    chosen, weights, gate = torch.empty(n, top, dtype=i32, device=DEV), torch.empty(n, top, device=DEV), torch.empty(n, device=DEV)
+    count, offset = torch.empty(E, dtype=i32, device=DEV), torch.empty(E + 1, dtype=i32, device=DEV)
+    order, place = torch.empty(pairs, dtype=i32, device=DEV), torch.empty(pairs, dtype=i32, device=DEV)
+    act, y, out = torch.empty(pairs, I, dtype=bf, device=DEV), torch.empty(pairs, W, device=DEV), torch.empty(n, W, device=DEV)
+    groups = args.groups
+    ops.moe_route(x, wr, wg, chosen, weights, gate, groups, max(1, groups // 2))
+    ops.moe_plan(chosen, count, offset, order, place)
+    used = int((count > 0).sum())
+    state = {"i": 0}
+
+    def nxt():
+        state["i"] = (state["i"] + 1) % copies
+        return state["i"]
+    hbm, tflops, src = peaks()
+    rows = [("router", lambda: ops.moe_route(x, wr, wg, chosen, weights, gate, groups, max(1, groups // 2)), n * W * 2 + (E + 1) * W * 4, 2.0 * n * (E + 1) * W),
+            ("pairs sorted by expert", lambda: ops.moe_plan(chosen, count, offset, order, place), pairs * 12, 0.0),
+            ("gate|up with the clamped unit", lambda: ops.moe_grouped(x, w_gu[nxt()], act, offset, order, top, True, 7.0, 1.702),
+             used * 2 * I * W * 2 + pairs * (W + I) * 2, 4.0 * pairs * I * W),
+            ("down", lambda: ops.moe_grouped(act, w_d[nxt()], y, offset, order, top, False), used * I * W * 2 + pairs * (I * 2 + W * 4), 2.0 * pairs * I * W),
+            ("weighted sum", lambda: ops.moe_combine(y, place, weights, None, None, out), pairs * W * 4 + n * W * 4, 0.0)]
+    if ops.tc_grouped_ok(x, w_gu[0]) and I % 8 == 0:
+        tiles = torch.empty(1 + 3 * ops.moe_row_tiles(pairs, E), dtype=i32, device=DEV)
+        ops.moe_plan(chosen, count, offset, order, place, tiles)
+        xs = torch.empty(pairs, W, dtype=bf, device=DEV)
+        rows += [("rows into sorted order", lambda: ops.moe_gather(x, order, top, xs), pairs * W * 4, 0.0),
+                 ("gate|up, clamped unit (tcgen05)", lambda: ops.gemm_bf16_tc_grouped(xs, w_gu[nxt()], act, tiles, True, 7.0, 1.702),
+                  used * 2 * I * W * 2 + pairs * (W + I) * 2, 4.0 * pairs * I * W),
+                 ("down (tcgen05)", lambda: ops.gemm_bf16_tc_grouped(act, w_d[nxt()], y, tiles, False),
+                  used * I * W * 2 + pairs * (I * 2 + W * 4), 2.0 * pairs * I * W)]
+    print(f"experts: {n} tokens, {E} experts ({used} used), top {top}, width {W}, ff {I}; peaks {src}: {hbm:.0f} GB/s, {tflops:.0f} TFLOP/s")
+    for name, fn, moved, flops in rows:
+        ms = timed(fn, args.iters)
+        floor = max(moved / (hbm * 1e6), flops / (tflops * 1e9))
+        print(f"  {name:32s} {ms * 1e3:9.1f} us   {moved / ms / 1e6:8.0f} GB/s   {flops / ms / 1e9:8.1f} TFLOP/s   {ms / max(floor, 1e-9):6.1f} x its floor")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m wllm_b200.kernels.cases", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -267,6 +314,13 @@ def main(argv=None) -> int:
     rc.add_argument("--vdim", type=int, default=256)
     rc.add_argument("--per-head", action="store_true", help="one decay per head (retention) instead of one per key channel")
     rc.add_argument("--no-segments", action="store_true", help="walk every portion in one go")
+    ex = sub.add_parser("experts")
+    ex.add_argument("--tokens", type=int, default=2048)
+    ex.add_argument("--experts", type=int, default=32)
+    ex.add_argument("--top", type=int, default=4)
+    ex.add_argument("--groups", type=int, default=4)
+    ex.add_argument("--width", type=int, default=2048)
+    ex.add_argument("--ff", type=int, default=1024)
     sm = sub.add_parser("sampling")
     sm.add_argument("--rows", type=int, default=8)
     sm.add_argument("--vocab", type=int, default=256000)
@@ -290,6 +344,8 @@ def main(argv=None) -> int:
         sampling(args)
     elif args.case == "recurrence":
         recurrence(args)
+    elif args.case == "experts":
+        experts(args)
     else:
         attention(args, decode=args.case == "attention-decode")
     return 0

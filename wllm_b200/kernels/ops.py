@@ -847,16 +847,28 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, w_gate, chosen: torch.Ten
                               top, groups, groups_kept, _stream()), f"moe_route(experts={E}, top={top}, groups={groups}/{groups_kept})")
 
 
-def moe_plan(chosen: torch.Tensor, count: torch.Tensor, offset: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+MOE_TILE_ROWS = 128      # rows of a row tile of the experts' products on the tensor-memory kernel
+
+
+def moe_row_tiles(pairs: int, experts: int) -> int:
+    """Most row tiles (MOE_TILE_ROWS rows of one expert each) that `pairs` sorted rows of `experts` experts can make."""
+    return -(-pairs // MOE_TILE_ROWS) + experts
+
+
+def moe_plan(chosen: torch.Tensor, count: torch.Tensor, offset: torch.Tensor, order: torch.Tensor, place: torch.Tensor,
+             tiles: torch.Tensor | None = None) -> None:
     """The (token, rank) pairs of `chosen` [n, top] sorted by expert, stably: count [E], offset [E + 1], order [pairs] (sorted
-    row -> pair), place [pairs] (pair -> sorted row)."""
-    _need_cuda(chosen, count, offset, order, place)
+    row -> pair), place [pairs] (pair -> sorted row).  `tiles` (int32, 1 + 3 * moe_row_tiles(pairs, E)): the table of row
+    tiles for gemm_bf16_tc_grouped: their number, then (expert, first sorted row, rows) a tile."""
+    _need_cuda(chosen, count, offset, order, place, tiles)
     pairs, E = chosen.numel(), count.shape[0]
     assert offset.shape == (E + 1,) and order.shape == place.shape == (pairs,)
     for t in (chosen, count, offset, order, place):
         assert t.dtype == torch.int32 and t.is_contiguous()
+    assert tiles is None or (tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.numel() >= 1 + 3 * moe_row_tiles(pairs, E))
     lib = load_family("moe")
-    _check(lib.wllm_moe_plan(_ptr(chosen), pairs, E, _ptr(count), _ptr(offset), _ptr(order), _ptr(place), _stream()), "moe_plan")
+    _check(lib.wllm_moe_plan_tiles(_ptr(chosen), pairs, E, _ptr(count), _ptr(offset), _ptr(order), _ptr(place), _ptr(tiles),
+                                   MOE_TILE_ROWS, _stream()), "moe_plan")
     global launches
     launches += 1
 
@@ -876,6 +888,42 @@ def moe_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offset: tor
     _check(lib.wllm_moe_grouped(_ptr(a), a.stride(0), _ptr(w), _ptr(out), _dt(a), 1 if gated else 0, pairs, N, K,
                                 _ptr(_int32(offset, "offset")), _ptr(_int32(order, "order")), E, top, c_float(limit), c_float(slope),
                                 _stream()), f"moe_grouped({pairs}x{N}x{K}, {E} experts)")
+    return out
+
+
+def moe_gather(x: torch.Tensor, order: torch.Tensor, top: int, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[order[r] // top]: the tokens' bfloat16 rows in the order of the sorted pairs."""
+    _need_cuda(x, order, out)
+    pairs, K = out.shape
+    assert x.dtype == out.dtype == torch.bfloat16 and x.stride(1) == 1 and out.is_contiguous() and x.shape[1] == K and order.shape == (pairs,)
+    lib = load_family("moe")
+    _check(lib.wllm_moe_gather(_ptr(x), x.stride(0), _ptr(_int32(order, "order")), top, _ptr(out), pairs, K, _stream()), "moe_gather")
+    return out
+
+
+def tc_grouped_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Shapes the grouped tensor-memory product takes: bfloat16, rows of A contiguous, K in steps of 8."""
+    return (a.dtype == torch.bfloat16 == w.dtype and a.dim() == 2 and w.dim() == 3 and a.is_contiguous() and w.is_contiguous()
+            and a.shape[1] == w.shape[2] and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_bf16_tc_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tiles: torch.Tensor, gated: bool, limit: float = 0.0,
+                         slope: float = 0.0) -> torch.Tensor:
+    """The experts' products on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu, grouped): a [rows, K] bfloat16 rows sorted by
+    expert, w [E, N, K] (or, gated, [E, 2N, K] = [gate; up]: out = the clamped gated unit, bfloat16 [rows, N]; else out float32
+    [rows, N]), `tiles` the table of row tiles that moe_plan left on the device."""
+    _need_cuda(a, w, out, tiles)
+    if not tc_grouped_ok(a, w):
+        raise KernelError("gemm_bf16_tc_grouped: contiguous bfloat16 operands with K in steps of 8")
+    rows, K = a.shape
+    E = w.shape[0]
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    assert out.shape == (rows, N) and out.is_contiguous() and out.dtype == (torch.bfloat16 if gated else torch.float32)
+    assert tiles.dtype == torch.int32 and tiles.numel() >= 1 + 3 * moe_row_tiles(rows, E)
+    lib = load_family("gemm_bf16_tc")
+    _check(lib.wllm_gemm_bf16_tc_grouped(_ptr(a), K, _ptr(w), K, _ptr(out), N, rows, N, K, E, 5 if gated else 1, _ptr(tiles),
+                                         moe_row_tiles(rows, E), _ptr(_status_word(a.device)), sm_count(), c_float(limit),
+                                         c_float(slope), _stream()), f"gemm_bf16_tc_grouped({rows}x{N}x{K}, {E} experts)")
     return out
 
 

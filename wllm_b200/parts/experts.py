@@ -24,6 +24,7 @@ from .base import FEED_FORWARDS, ParamSpec, branch_pair, spec as make_spec
 @FEED_FORWARDS.register("routed_experts")
 class RoutedExperts:
     graph_safe = True
+    TC_FROM_PAIRS = 1024       # (token, expert) pairs from which the experts' products run on the tensor-memory kernel
 
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.E, self.top = int(spec.num_experts), int(spec.top)
@@ -76,11 +77,21 @@ class RoutedExperts:
         index = ctx.buffer("moe_index", (2 * self.E + 1 + 2 * pairs,), torch.int32)
         count, offset = index[:self.E], index[self.E:2 * self.E + 1]
         order, place = index[2 * self.E + 1:2 * self.E + 1 + pairs], index[2 * self.E + 1 + pairs:]
-        ops.moe_plan(chosen, count, offset, order, place)
         act = ctx.buffer("moe_act", (pairs, self.inter), self.model_dtype)
-        ops.moe_grouped(x, self.w_gu, act, offset, order, top, True, self.limit, self.slope)
         y = ctx.buffer("moe_y", (pairs, H), torch.float32)
-        ops.moe_grouped(act, self.w_down, y, offset, order, top, False)
+        # Many rows (portions of prompts): the products run on the tensor-memory kernel over row tiles of one expert each, on
+        # the tokens' rows copied into sorted order.  Few rows (decoding) are bound by streaming the experts' weights, which
+        # the kernel on mma.sync does from rows gathered on the fly.
+        if pairs >= self.TC_FROM_PAIRS and x.dtype == torch.bfloat16 and ops.tc_grouped_ok(x, self.w_gu) and self.inter % 8 == 0:
+            tiles = ctx.buffer("moe_tiles", (1 + 3 * ops.moe_row_tiles(pairs, self.E),), torch.int32)
+            ops.moe_plan(chosen, count, offset, order, place, tiles)
+            rows = ops.moe_gather(x, order, top, ctx.buffer("moe_rows", (pairs, H), self.model_dtype))
+            ops.gemm_bf16_tc_grouped(rows, self.w_gu, act, tiles, True, self.limit, self.slope)
+            ops.gemm_bf16_tc_grouped(act, self.w_down, y, tiles, False)
+        else:
+            ops.moe_plan(chosen, count, offset, order, place)
+            ops.moe_grouped(x, self.w_gu, act, offset, order, top, True, self.limit, self.slope)
+            ops.moe_grouped(act, self.w_down, y, offset, order, top, False)
         shared = branch_pair(self.shared(x, ctx)) if self.shared is not None else None
         out = ctx.buffer("moe_out", (n, H), torch.float32)
         return ops.moe_combine(y, place, weights, shared, gate, out)
