@@ -676,10 +676,20 @@ def taritar_kernel_table(size: dict, pk: dict, T: int, batch: int, context: int)
         w_gu, w_d = rnd(E, 2 * eff, W, dtype=bf, scale=0.02), rnd(E, W, eff, dtype=bf, scale=0.02)
         act, y = torch.empty(pairs, eff, dtype=bf, device=dev), torch.empty(pairs, W, device=dev)
         used = min(E, pairs)           # experts whose weights a step reads at most
-        row(f"{tag}/experts: gate|up with the clamped unit (grouped)", lambda: ops.moe_grouped(x, w_gu, act, offset, order, top, True, 7.0, 1.702),
+        row(f"{tag}/experts: gate|up with the clamped unit (grouped, mma.sync)", lambda: ops.moe_grouped(x, w_gu, act, offset, order, top, True, 7.0, 1.702),
             used * 2 * eff * W * 2 + pairs * (W + eff) * 2, 4.0 * pairs * eff * W)
-        row(f"{tag}/experts: down (grouped)", lambda: ops.moe_grouped(act, w_d, y, offset, order, top, False),
+        row(f"{tag}/experts: down (grouped, mma.sync)", lambda: ops.moe_grouped(act, w_d, y, offset, order, top, False),
             used * eff * W * 2 + pairs * (eff * 2 + W * 4), 2.0 * pairs * eff * W)
+        if pairs >= 1024:      # portions of prompts: the experts' products on the tensor-memory kernel, over rows copied into sorted order
+            tiles = torch.empty(1 + 3 * ops.moe_row_tiles(pairs, E), dtype=i32, device=dev)
+            scratch = torch.empty(ops.MOE_PLAN_SEGMENTS * E, dtype=i32, device=dev)
+            row(f"{tag}/pairs sorted by expert, with the table of row tiles", lambda: ops.moe_plan(chosen, count, offset, order, place, tiles, scratch), pairs * 4 * 3)
+            xs = torch.empty(pairs, W, dtype=bf, device=dev)
+            row(f"{tag}/experts: the tokens' rows into sorted order", lambda: ops.moe_gather(x, order, top, xs), pairs * W * 4)
+            row(f"{tag}/experts: gate|up with the clamped unit (grouped, tensor memory)", lambda: ops.gemm_bf16_tc_grouped(xs, w_gu, act, tiles, True, 7.0, 1.702),
+                used * 2 * eff * W * 2 + pairs * (W + eff) * 2, 4.0 * pairs * eff * W)
+            row(f"{tag}/experts: down (grouped, tensor memory)", lambda: ops.gemm_bf16_tc_grouped(act, w_d, y, tiles, False),
+                used * eff * W * 2 + pairs * (eff * 2 + W * 4), 2.0 * pairs * eff * W)
         shared, o32 = rnd(n, W, dtype=bf), torch.empty(n, W, device=dev)
         row(f"{tag}/experts' outputs weighted and summed, shared unit gated and added", lambda: ops.moe_combine(y, place, weights, (shared, 0), gate, o32),
             pairs * W * 4 + n * W * (2 + 4))

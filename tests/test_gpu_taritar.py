@@ -474,7 +474,7 @@ def test_interleaved_rotation_of_many_rows_is_that_of_few(hd, rot):
     assert torch.equal(q2.cpu(), outs[0][0])
 
 
-@pytest.mark.parametrize("n,E,top,H,I", [(300, 6, 4, 72, 24), (700, 5, 2, 64, 104), (130, 40, 8, 128, 264)])
+@pytest.mark.parametrize("n,E,top,H,I", [(300, 6, 4, 72, 24), (700, 5, 4, 64, 104), (130, 40, 8, 128, 264)])
 def test_experts_on_the_tensor_memory_product(n, E, top, H, I):
     """Many rows: the tokens' rows copied into sorted order, row tiles of 128 rows of one expert each from the table that the
     plan leaves on the device (experts with no row, with a few and with more than a tile), both products on tcgen05."""
@@ -503,7 +503,11 @@ def test_experts_on_the_tensor_memory_product(n, E, top, H, I):
     count, offset = torch.empty(E, dtype=torch.int32, device=DEV), torch.empty(E + 1, dtype=torch.int32, device=DEV)
     order, place = torch.empty(pairs, dtype=torch.int32, device=DEV), torch.empty(pairs, dtype=torch.int32, device=DEV)
     tiles = torch.full((1 + 3 * ops.moe_row_tiles(pairs, E),), -7, dtype=torch.int32, device=DEV)
-    ops.moe_plan(chosen.to(DEV), count, offset, order, place, tiles)
+    ops.moe_plan(chosen.to(DEV), count, offset, order, place)
+    one_warp = [t.clone() for t in (count, offset, order, place)]
+    scratch = torch.empty(ops.MOE_PLAN_SEGMENTS * E, dtype=torch.int32, device=DEV) if n == 700 else None     # 2,800 pairs: in segments
+    ops.moe_plan(chosen.to(DEV), count, offset, order, place, tiles, scratch)
+    assert all(torch.equal(a, b) for a, b in zip(one_warp, (count, offset, order, place)))
     table = tiles.cpu().tolist()
     counts = torch.bincount(chosen.reshape(-1).long(), minlength=E).tolist()
     assert table[0] == sum(-(-c // 128) for c in counts) and counts[-1] == 0 and (max(counts) > 128) == (n >= 300)

@@ -122,35 +122,43 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
     }
 }
 
-// grid: E warps (4 a CTA).  count[e] = pairs whose expert is e.
-__global__ void __launch_bounds__(128) moe_count_kernel(const int* __restrict__ chosen, int pairs, int E, int* __restrict__ count) {
+// The pair list is cut into `segs` segments of seg_len pairs (a multiple of 128) so that long lists are scanned by segs
+// warps an expert.  grid: E * segs warps (4 a CTA).  partial[seg * E + e] = pairs of the segment whose expert is e.
+__global__ void __launch_bounds__(128) moe_count_kernel(const int* __restrict__ chosen, int pairs, int E, int segs, int seg_len,
+                                                        int* __restrict__ partial) {
     pdl_begin();
-    const int e = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (e >= E) return;
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= E * segs) return;
+    const int e = w % E, seg = w / E;
+    const int lo = seg * seg_len, hi = min(pairs, lo + seg_len);
     int c = 0;
-    for (int p0 = 0; p0 < pairs; p0 += 128) {          // four loads in flight a lane
+    for (int p0 = lo; p0 < hi; p0 += 128) {          // four loads in flight a lane
         bool mine[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) { const int p = p0 + 32 * u + lane; mine[u] = p < pairs && chosen[p] == e; }
+        for (int u = 0; u < 4; ++u) { const int p = p0 + 32 * u + lane; mine[u] = p < hi && chosen[p] == e; }
 #pragma unroll
         for (int u = 0; u < 4; ++u) c += __popc(__ballot_sync(0xffffffffu, mine[u]));
     }
-    if (lane == 0) count[e] = c;
+    if (lane == 0) partial[seg * E + e] = c;
 }
 
-// offset[e] = count[0] + .. + count[e-1] (offset[E] = pairs); the pairs of expert e in ascending order fill the sorted
-// rows from offset[e]: sorted[r] = pair, place[pair] = r.
+// count[e] = pairs of expert e, offset[e] = count[0] + .. + count[e-1] (offset[E] = pairs); the pairs of expert e in ascending
+// order fill the sorted rows from offset[e]: sorted[r] = pair, place[pair] = r.  The warp of (expert, segment) places its
+// segment's pairs behind those of the segments before it.
 // With `tiles` (null: none): the table of row tiles of `tile_rows` rows of one expert each, for the products that walk it:
 // tiles[0] = their number, then (expert, first sorted row, rows) a tile, expert by expert.
-__global__ void __launch_bounds__(128) moe_place_kernel(const int* __restrict__ chosen, int pairs, int E, const int* __restrict__ count,
+__global__ void __launch_bounds__(128) moe_place_kernel(const int* __restrict__ chosen, int pairs, int E, int segs, int seg_len,
+                                                        const int* __restrict__ partial, int* __restrict__ count,
                                                         int* __restrict__ offset, int* __restrict__ sorted, int* __restrict__ place,
                                                         int* __restrict__ tiles, int tile_rows) {
     pdl_begin();
-    const int e = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (e >= E) return;
+    const int w = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= E * segs) return;
+    const int e = w % E, seg = w / E;
     int before = 0, tiles_before = 0;
     for (int j = lane; j < e; j += 32) {
-        const int c = count[j];
+        int c = 0;
+        for (int s2 = 0; s2 < segs; ++s2) c += partial[s2 * E + j];
         before += c;
         if (tiles) tiles_before += (c + tile_rows - 1) / tile_rows;
     }
@@ -158,23 +166,33 @@ __global__ void __launch_bounds__(128) moe_place_kernel(const int* __restrict__ 
         before += __shfl_xor_sync(0xffffffffu, before, o);
         tiles_before += __shfl_xor_sync(0xffffffffu, tiles_before, o);
     }
-    if (lane == 0) {
-        offset[e] = before;
-        if (e == E - 1) offset[E] = before + count[e];
+    int mine_total = 0, mine_before = 0;
+    for (int s2 = 0; s2 < segs; ++s2) {
+        const int c = partial[s2 * E + e];
+        mine_total += c;
+        if (s2 < seg) mine_before += c;
     }
-    if (tiles) {
-        const int mine = count[e], n_tiles = (mine + tile_rows - 1) / tile_rows;
-        for (int t = lane; t < n_tiles; t += 32) {
-            int* entry = tiles + 1 + 3 * (tiles_before + t);
-            entry[0] = e; entry[1] = before + t * tile_rows; entry[2] = min(tile_rows, mine - t * tile_rows);
+    if (seg == 0) {
+        if (lane == 0) {
+            count[e] = mine_total;
+            offset[e] = before;
+            if (e == E - 1) offset[E] = before + mine_total;
         }
-        if (e == E - 1 && lane == 0) tiles[0] = tiles_before + n_tiles;
+        if (tiles) {
+            const int n_tiles = (mine_total + tile_rows - 1) / tile_rows;
+            for (int t = lane; t < n_tiles; t += 32) {
+                int* entry = tiles + 1 + 3 * (tiles_before + t);
+                entry[0] = e; entry[1] = before + t * tile_rows; entry[2] = min(tile_rows, mine_total - t * tile_rows);
+            }
+            if (e == E - 1 && lane == 0) tiles[0] = tiles_before + n_tiles;
+        }
     }
-    int at = before;
-    for (int p0 = 0; p0 < pairs; p0 += 128) {          // four loads in flight a lane; the pairs still go in ascending order
+    int at = before + mine_before;
+    const int lo = seg * seg_len, hi = min(pairs, lo + seg_len);
+    for (int p0 = lo; p0 < hi; p0 += 128) {          // four loads in flight a lane; the pairs still go in ascending order
         bool mine[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) { const int p = p0 + 32 * u + lane; mine[u] = p < pairs && chosen[p] == e; }
+        for (int u = 0; u < 4; ++u) { const int p = p0 + 32 * u + lane; mine[u] = p < hi && chosen[p] == e; }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const unsigned b = __ballot_sync(0xffffffffu, mine[u]);
@@ -434,23 +452,43 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
 // out[t][c] = sum_k weights[t][k] * y[place[t top + k]][c]  (+ gate[t] * shared[t][c], shared a tensor of TS or `parts`
 // 32-bit partial sums added in order first)
 template <typename TS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights, int top,
                    const TS* __restrict__ shared, int parts, size_t part_stride, const float* __restrict__ gate,
                    float* __restrict__ out, int H) {
+    __shared__ int s_place[64];
+    __shared__ float s_weight[64];
     pdl_begin();
     const int t = blockIdx.x;
+    for (int k = threadIdx.x; k < min(top, 64); k += blockDim.x) { s_place[k] = place[(size_t)t * top + k]; s_weight[k] = weights[(size_t)t * top + k]; }
+    __syncthreads();
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float v = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const float term = weights[(size_t)t * top + k] * y[(size_t)place[(size_t)t * top + k] * H + c];
-            v = k == 0 ? term : v + term;
+        for (int k0 = 0; k0 < top; k0 += 8) {          // eight of the experts' rows in flight; the sum is in rank order
+            float term[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int k = k0 + u;
+                term[u] = 0.f;
+                if (k < top) {
+                    const int row = k < 64 ? s_place[k] : place[(size_t)t * top + k];
+                    const float wk = k < 64 ? s_weight[k] : weights[(size_t)t * top + k];
+                    term[u] = wk * y[(size_t)row * H + c];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (k0 + u < top) v = (k0 + u == 0) ? term[u] : v + term[u];
         }
         if (shared != nullptr) {
             float s = 0.f;
-            for (int p = 0; p < parts; ++p) {
-                const float part = to_f32(shared[(size_t)p * part_stride + (size_t)t * H + c]);
-                s = p == 0 ? part : s + part;
+            for (int p0 = 0; p0 < parts; p0 += 16) {
+                float part[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) part[u] = p0 + u < parts ? to_f32(shared[(size_t)(p0 + u) * part_stride + (size_t)t * H + c]) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 16; ++u)
+                    if (p0 + u < parts) s = (p0 + u == 0) ? part[u] : s + part[u];
             }
             v = fmaf(gate[t], s, v);
         }
@@ -486,19 +524,25 @@ WLLM_API int wllm_moe_route(const void* h, int dtype, const float* w_router, con
 }
 
 // count [E], offset [E + 1], sorted [pairs], place [pairs]
-// tiles (null: none): 1 + 3 * (ceil(pairs / tile_rows) + E) ints, the table of row tiles (see moe_place_kernel)
+constexpr int MOE_PLAN_SEGMENTS = 8;
+
+// tiles (null: none): 1 + 3 * (ceil(pairs / tile_rows) + E) ints, the table of row tiles (see moe_place_kernel).
+// scratch (null: none): MOE_PLAN_SEGMENTS * E ints; with it, long pair lists are scanned by that many warps an expert.
 WLLM_API int wllm_moe_plan_tiles(const int* chosen, int pairs, int E, int* count, int* offset, int* sorted, int* place, int* tiles,
-                                 int tile_rows, cudaStream_t stream) {
+                                 int tile_rows, int* scratch, cudaStream_t stream) {
     if (pairs <= 0) return WLLM_OK;
     if (E <= 0 || E > MOE_MAX_EXPERTS || (tiles != nullptr && tile_rows < 1)) return WLLM_BAD_SIZE;
-    const int st = wllm_launch(moe_count_kernel, (E + 3) / 4, 128, 0, stream, chosen, pairs, E, count);
+    const int segs = (scratch != nullptr && pairs >= 2048) ? MOE_PLAN_SEGMENTS : 1;
+    const int seg_len = ((pairs + segs - 1) / segs + 127) / 128 * 128;
+    int* partial = segs > 1 ? scratch : count;           // one segment: the partial counts are the counts
+    const int st = wllm_launch(moe_count_kernel, (E * segs + 3) / 4, 128, 0, stream, chosen, pairs, E, segs, seg_len, partial);
     if (st != WLLM_OK) return st;
-    return wllm_launch(moe_place_kernel, (E + 3) / 4, 128, 0, stream, chosen, pairs, E, (const int*)count, offset, sorted, place, tiles,
-                       tile_rows);
+    return wllm_launch(moe_place_kernel, (E * segs + 3) / 4, 128, 0, stream, chosen, pairs, E, segs, seg_len, (const int*)partial, count,
+                       offset, sorted, place, tiles, tile_rows);
 }
 
 WLLM_API int wllm_moe_plan(const int* chosen, int pairs, int E, int* count, int* offset, int* sorted, int* place, cudaStream_t stream) {
-    return wllm_moe_plan_tiles(chosen, pairs, E, count, offset, sorted, place, nullptr, 0, stream);
+    return wllm_moe_plan_tiles(chosen, pairs, E, count, offset, sorted, place, nullptr, 0, nullptr, stream);
 }
 
 // out[r] = x[sorted[r] / top]: the tokens' rows in the order of the sorted pairs (K elements of 2 bytes, K in steps of 8)
@@ -554,7 +598,8 @@ WLLM_API int wllm_moe_combine(const float* y, const int* place, const float* wei
                               int parts, long long part_stride, const float* gate, float* out, int n, int H, cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (H <= 0 || top < 1 || parts < 1 || (shared != nullptr && gate == nullptr)) return WLLM_BAD_SIZE;
-    const int threads = H >= 1024 ? 256 : 128;
+    int threads = H >= 1024 ? 256 : 128;
+    if (n <= 64) threads = H >= 2048 ? 1024 : (H >= 1024 ? 512 : threads);      // few rows: a thread a column or two, every load in flight
     if (shared == nullptr || shared_dtype == WLLM_F32)
         return wllm_launch(moe_combine_kernel<float>, n, threads, 0, stream, y, place, weights, top, (const float*)shared, parts,
                            (size_t)part_stride, gate, out, H);

@@ -855,20 +855,25 @@ def moe_row_tiles(pairs: int, experts: int) -> int:
     return -(-pairs // MOE_TILE_ROWS) + experts
 
 
+MOE_PLAN_SEGMENTS = 8     # warps an expert that scan a long list of pairs (csrc/moe.cu)
+
+
 def moe_plan(chosen: torch.Tensor, count: torch.Tensor, offset: torch.Tensor, order: torch.Tensor, place: torch.Tensor,
-             tiles: torch.Tensor | None = None) -> None:
+             tiles: torch.Tensor | None = None, scratch: torch.Tensor | None = None) -> None:
     """The (token, rank) pairs of `chosen` [n, top] sorted by expert, stably: count [E], offset [E + 1], order [pairs] (sorted
     row -> pair), place [pairs] (pair -> sorted row).  `tiles` (int32, 1 + 3 * moe_row_tiles(pairs, E)): the table of row
-    tiles for gemm_bf16_tc_grouped: their number, then (expert, first sorted row, rows) a tile."""
-    _need_cuda(chosen, count, offset, order, place, tiles)
+    tiles for gemm_bf16_tc_grouped: their number, then (expert, first sorted row, rows) a tile.  `scratch` (int32,
+    MOE_PLAN_SEGMENTS * E): with it a long list is scanned by several warps an expert; the result is the same."""
+    _need_cuda(chosen, count, offset, order, place, tiles, scratch)
     pairs, E = chosen.numel(), count.shape[0]
     assert offset.shape == (E + 1,) and order.shape == place.shape == (pairs,)
     for t in (chosen, count, offset, order, place):
         assert t.dtype == torch.int32 and t.is_contiguous()
     assert tiles is None or (tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.numel() >= 1 + 3 * moe_row_tiles(pairs, E))
     lib = load_family("moe")
+    assert scratch is None or (scratch.dtype == torch.int32 and scratch.is_contiguous() and scratch.numel() >= MOE_PLAN_SEGMENTS * E)
     _check(lib.wllm_moe_plan_tiles(_ptr(chosen), pairs, E, _ptr(count), _ptr(offset), _ptr(order), _ptr(place), _ptr(tiles),
-                                   MOE_TILE_ROWS, _stream()), "moe_plan")
+                                   MOE_TILE_ROWS, _ptr(scratch), _stream()), "moe_plan")
     global launches
     launches += 1
 

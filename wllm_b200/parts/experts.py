@@ -84,7 +84,7 @@ class RoutedExperts:
         # the kernel on mma.sync does from rows gathered on the fly.
         if pairs >= self.TC_FROM_PAIRS and x.dtype == torch.bfloat16 and ops.tc_grouped_ok(x, self.w_gu) and self.inter % 8 == 0:
             tiles = ctx.buffer("moe_tiles", (1 + 3 * ops.moe_row_tiles(pairs, self.E),), torch.int32)
-            ops.moe_plan(chosen, count, offset, order, place, tiles)
+            ops.moe_plan(chosen, count, offset, order, place, tiles, ctx.buffer("moe_plan", (ops.MOE_PLAN_SEGMENTS * self.E,), torch.int32))
             rows = ops.moe_gather(x, order, top, ctx.buffer("moe_rows", (pairs, H), self.model_dtype))
             ops.gemm_bf16_tc_grouped(rows, self.w_gu, act, tiles, True, self.limit, self.slope)
             ops.gemm_bf16_tc_grouped(act, self.w_down, y, tiles, False)
