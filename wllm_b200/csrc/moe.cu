@@ -451,6 +451,34 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
 
 // out[t][c] = sum_k weights[t][k] * y[place[t top + k]][c]  (+ gate[t] * shared[t][c], shared a tensor of TS or `parts`
 // 32-bit partial sums added in order first)
+// Many rows: a CTA of a few warps a token, one load after the other a thread (other CTAs hide the wait).
+template <typename TS>
+__global__ void __launch_bounds__(256)
+moe_combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights, int top,
+                        const TS* __restrict__ shared, int parts, size_t part_stride, const float* __restrict__ gate,
+                        float* __restrict__ out, int H) {
+    pdl_begin();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float term = weights[(size_t)t * top + k] * y[(size_t)place[(size_t)t * top + k] * H + c];
+            v = k == 0 ? term : v + term;
+        }
+        if (shared != nullptr) {
+            float s = 0.f;
+            for (int p = 0; p < parts; ++p) {
+                const float part = to_f32(shared[(size_t)p * part_stride + (size_t)t * H + c]);
+                s = p == 0 ? part : s + part;
+            }
+            v = fmaf(gate[t], s, v);
+        }
+        out[(size_t)t * H + c] = v;
+    }
+}
+
+// Few rows (a decode step): a thread a column or two, the experts' rows and the shared unit's partial sums all in flight.  The
+// arithmetic of an output element is that of the kernel above.
 template <typename TS>
 __global__ void __launch_bounds__(1024)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights, int top,
@@ -600,11 +628,12 @@ WLLM_API int wllm_moe_combine(const float* y, const int* place, const float* wei
     if (H <= 0 || top < 1 || parts < 1 || (shared != nullptr && gate == nullptr)) return WLLM_BAD_SIZE;
     int threads = H >= 1024 ? 256 : 128;
     if (n <= 64) threads = H >= 2048 ? 1024 : (H >= 1024 ? 512 : threads);      // few rows: a thread a column or two, every load in flight
+    const bool few = n <= 64;
     if (shared == nullptr || shared_dtype == WLLM_F32)
-        return wllm_launch(moe_combine_kernel<float>, n, threads, 0, stream, y, place, weights, top, (const float*)shared, parts,
-                           (size_t)part_stride, gate, out, H);
+        return wllm_launch(few ? moe_combine_kernel<float> : moe_combine_rows_kernel<float>, n, threads, 0, stream, y, place, weights, top,
+                           (const float*)shared, parts, (size_t)part_stride, gate, out, H);
     if (shared_dtype == WLLM_BF16 && parts == 1)
-        return wllm_launch(moe_combine_kernel<bf16>, n, threads, 0, stream, y, place, weights, top, (const bf16*)shared, parts,
-                           (size_t)part_stride, gate, out, H);
+        return wllm_launch(few ? moe_combine_kernel<bf16> : moe_combine_rows_kernel<bf16>, n, threads, 0, stream, y, place, weights, top,
+                           (const bf16*)shared, parts, (size_t)part_stride, gate, out, H);
     return WLLM_BAD_DTYPE;
 }
