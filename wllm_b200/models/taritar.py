@@ -62,7 +62,7 @@ def taritar_plan(cfg: TaritarConfig) -> ModelPlan:
         if S is None:
             return spec("rmsnorm", weight=name, eps=cfg.eps)
         return spec("hyper_rmsnorm", weight=name, eps=cfg.eps, streams=S, connections=connections)
-    blocks, runs, writer = [], [], {}
+    blocks, runs = [], []
     for i, layer in enumerate(cfg.layers):
         p = f"l{i}."
         options = dict(norm_in=norm(p + "norm1", p + "hc1."), mixer=_attention(p + "mix.", layer["mixer"]))
