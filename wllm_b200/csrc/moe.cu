@@ -462,14 +462,15 @@ moe_combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ pla
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float v = 0.f;
         for (int k = 0; k < top; ++k) {
-            const float term = weights[(size_t)t * top + k] * y[(size_t)place[(size_t)t * top + k] * H + c];
-            v = k == 0 ? term : v + term;
+            // every product and sum rounded on its own, in both kernels: one result whichever serves the row
+            const float term = __fmul_rn(weights[(size_t)t * top + k], y[(size_t)place[(size_t)t * top + k] * H + c]);
+            v = k == 0 ? term : __fadd_rn(v, term);
         }
         if (shared != nullptr) {
             float s = 0.f;
             for (int p = 0; p < parts; ++p) {
                 const float part = to_f32(shared[(size_t)p * part_stride + (size_t)t * H + c]);
-                s = p == 0 ? part : s + part;
+                s = p == 0 ? part : __fadd_rn(s, part);
             }
             v = fmaf(gate[t], s, v);
         }
@@ -501,12 +502,12 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
                 if (k < top) {
                     const int row = k < 64 ? s_place[k] : place[(size_t)t * top + k];
                     const float wk = k < 64 ? s_weight[k] : weights[(size_t)t * top + k];
-                    term[u] = wk * y[(size_t)row * H + c];
+                    term[u] = __fmul_rn(wk, y[(size_t)row * H + c]);
                 }
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u)
-                if (k0 + u < top) v = (k0 + u == 0) ? term[u] : v + term[u];
+                if (k0 + u < top) v = (k0 + u == 0) ? term[u] : __fadd_rn(v, term[u]);
         }
         if (shared != nullptr) {
             float s = 0.f;
@@ -516,7 +517,7 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
                 for (int u = 0; u < 16; ++u) part[u] = p0 + u < parts ? to_f32(shared[(size_t)(p0 + u) * part_stride + (size_t)t * H + c]) : 0.f;
 #pragma unroll
                 for (int u = 0; u < 16; ++u)
-                    if (p0 + u < parts) s = (p0 + u == 0) ? part[u] : s + part[u];
+                    if (p0 + u < parts) s = (p0 + u == 0) ? part[u] : __fadd_rn(s, part[u]);
             }
             v = fmaf(gate[t], s, v);
         }
