@@ -224,8 +224,8 @@ def test_clamped_gated_unit_and_tanh_cap(dtype):
     assert (out.cpu().double() - want).abs().max() < (1e-6 if dtype == torch.float32 else 0.02)
     assert float(want.min()) < -0.2 and float((gu.double()[:, :40] > limit).float().mean()) > 0.1      # both clamps bite
     x = torch.randn(7, 33, generator=g) * 40
-    capped = ops.tanh_cap(x.to(DEV).clone(), 15.0)
-    assert (capped.cpu().double() - 15.0 * torch.tanh(x.double() / 15.0)).abs().max() < 1e-5
+    capped = ops.tanh_cap(x.to(DEV).clone(), 11.0)
+    assert (capped.cpu().double() - 11.0 * torch.tanh(x.double() / 11.0)).abs().max() < 1e-5
 
 
 def paged(keys, values, page_size, order_seed):
@@ -260,7 +260,7 @@ def plain_attention_rows(q, k, v, positions, scale, cap, size, keep):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("size,keep,cap", [(40, 5, 6.0), (96, 33, 0.0), (16, 16, 20.0), (8, 70, 4.0), (64, 0, 2.5), (130, 1, 0.0)])
+@pytest.mark.parametrize("size,keep,cap", [(40, 5, 6.0), (90, 33, 0.0), (16, 16, 18.0), (8, 70, 4.0), (64, 0, 2.5), (130, 1, 0.0)])
 def test_attention_with_a_cap_and_kept_first_keys_at_every_edge(size, keep, cap, dtype):
     """One key at a time is made to stand out (a key along the query, long enough to take all the weight when it is seen)
     just inside and just outside the window and the kept keys, for rows in a prompt's portion and for a single decoded
@@ -316,7 +316,7 @@ def test_attention_with_a_cap_and_kept_first_keys_at_every_edge(size, keep, cap,
         assert (moved > 0.05) == (edge == n0 - size + 1)
 
 
-@pytest.mark.parametrize("E,top,groups,kept", [(8, 2, 4, 2), (12, 4, 4, 3), (6, 3, 2, 1), (5, 1, 1, 1), (64, 6, 8, 3), (7, 7, 1, 1)])
+@pytest.mark.parametrize("E,top,groups,kept", [(8, 2, 4, 2), (15, 4, 5, 3), (6, 3, 2, 1), (5, 1, 1, 1), (64, 6, 8, 3), (7, 7, 1, 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_the_router_chooses_by_groups(E, top, groups, kept, dtype):
     from wllm_b200.kernels import ops
@@ -381,7 +381,7 @@ def test_experts_as_grouped_products(n, E, top, H, I, dtype):
 
 
 @pytest.mark.parametrize("hd", [32, 48, 64, 128])
-@pytest.mark.parametrize("size,keep,cap", [(40, 5, 6.0), (96, 33, 0.0), (16, 16, 20.0), (8, 70, 4.0), (64, 0, 2.5), (130, 1, 0.0), (100, 64, 3.0)])
+@pytest.mark.parametrize("size,keep,cap", [(40, 5, 6.0), (90, 33, 0.0), (16, 16, 18.0), (8, 70, 4.0), (64, 0, 2.5), (130, 1, 0.0), (100, 64, 3.0)])
 def test_tensor_core_attention_with_a_cap_and_kept_first_keys(size, keep, cap, hd):
     """The bfloat16 kernels on mma.sync that walk a list of key tiles (the kept keys' tiles, then the window's): a prompt's
     portion and decoded rows, with one key standing out at every edge, pages in scrambled order, page sizes 16 and 64, keys
@@ -392,7 +392,7 @@ def test_tensor_core_attention_with_a_cap_and_kept_first_keys(size, keep, cap, h
     scale = 0.4 * (16 / hd) ** 0.5
     k = torch.randn(L, G, hd, generator=g).to(dtype)
     v = torch.randn(L, G, hd, generator=g).to(dtype)
-    n0 = 236
+    n0 = 236 if hd != 128 else 90          # head size 128 and more than 128 rows: the prompt's rows run on pairs of CTAs (tcgen05)
     positions = list(range(n0, L))
     q = torch.randn(len(positions), H, hd, generator=g).to(dtype)
     one = lambda x: torch.tensor([x], dtype=torch.int32, device=DEV)
@@ -440,7 +440,7 @@ def test_the_clamped_unit_in_the_products_epilogue(M):
     assert ops.tc_gemm_status(DEV) == 0
 
 
-@pytest.mark.parametrize("hd,rot", [(48, 48), (128, 64), (32, 16)])
+@pytest.mark.parametrize("hd,rot", [(80, 80), (128, 64), (32, 16)])
 def test_interleaved_rotation_of_many_rows_is_that_of_few(hd, rot):
     """A prompt of many bfloat16 rows takes a kernel of its own (a CTA a token, 16-byte loads); its bits are those of the
     kernel that serves few rows, and both match the plain rotation of the pairs (2i, 2i + 1)."""

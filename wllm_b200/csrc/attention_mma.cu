@@ -1081,11 +1081,13 @@ WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void
 #if (HEAD_DIM % 64 == 0)
 #if (HEAD_DIM % 128 == 0)
     // more than one tile of 128 rows in the longest request: pairs of CTAs on 256-row tiles
-    if (!listed && use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+    // (the pair kernel walks a list of key tiles too and takes the cap; the one-CTA tensor-memory kernel does not)
+    if (use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         const int pair_tiles = (max_q_len * (nq / nkv) + 2 * TC_BM - 1) / (2 * TC_BM);
         return wllm_launch(prefill_pair_kernel, dim3(2 * nkv, requests, pair_tiles), TC_THREADS, PR_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
-                           block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status, sinks);
+                           block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status, sinks,
+                           cap * LOG2E, keep);
     }
 #endif
     if (!listed && use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {

@@ -416,7 +416,7 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                     const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                     const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
-                    int skip_single, int* __restrict__ status, const float* __restrict__ sinks) {
+                    int skip_single, int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
     // grid (2 x key/value heads, requests, tiles): the pairs start in the order x, y, z, the tiles that walk the most
@@ -443,8 +443,15 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
     // the keys that the pair's 256 rows see
     const int last_row = min(rows, (tile + 1) * 2 * TC_BM) - 1;
     const int pos_hi = pos0 + last_row / rep, pos_lo = pos0 + (tile * 2 * TC_BM) / rep;
-    const int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, key_hi = pos_hi + 1;
-    const int t0 = key_lo / PR_BN, t1 = (key_hi + PR_BN - 1) / PR_BN, T = t1 - t0;
+    int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, kept_cta = 0;
+    const int key_hi = pos_hi + 1;
+    // `keep` > 0: a sequence's first keys stay visible behind the window.  Where they touch the window the keys are one run from
+    // 0; else the tiles of the kept keys that lie before the window's first tile are walked first: place n of the walk is
+    // tile n, or t0 + n - head_tiles.  `capl` > 0: scores (log2 units) become capl * tanh(score / capl).
+    if (keep > 0) { if (key_lo <= keep) key_lo = 0; else kept_cta = keep; }
+    const int t0 = key_lo / PR_BN, t1 = (key_hi + PR_BN - 1) / PR_BN;
+    const int head_tiles = kept_cta > 0 ? min((kept_cta + PR_BN - 1) / PR_BN, t0) : 0, T = head_tiles + t1 - t0;
+    auto tile_of = [&](int n) { return n < head_tiles ? n : t0 + n - head_tiles; };
     const int page_shift = 31 - __clz(page_size);
     const int* table = block_table + (size_t)r * max_pages;
 
@@ -483,7 +490,7 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
             bool ok = true;
             int n = 0, edges = 0;
             for (; n < T && ok; ++n) {
-                const int s = n % PR_STAGES, ph = (n / PR_STAGES) & 1, tile_start = (t0 + n) * PR_BN + row_lo;
+                const int s = n % PR_STAGES, ph = (n / PR_STAGES) & 1, tile_start = tile_of(n) * PR_BN + row_lo;
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
                 const uint32_t bar = full0 + 8 * s, dst = ring + s * stage_bytes;
                 // A value tile that reaches past the request's last key (or in front of the window's first) holds, in
@@ -491,8 +498,8 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                 // number is no zero.  Such a tile (the last of a request's last rows) lands on a barrier of this CTA's
                 // own, its stray rows are cleared, and only then is it announced on the pair's barrier, by a plain
                 // arrival in place of the byte count.
-                const int key0 = (t0 + n) * PR_BN;
-                const bool edge = kv && (key0 + PR_BN > ctx || key0 < key_lo);
+                const int key0 = tile_of(n) * PR_BN;
+                const bool edge = kv && (key0 + PR_BN > ctx || key0 < key_lo);      // (a tile of kept keys lies before key_lo)
                 if (edge) mbar_expect_tx(v_edge, stage_bytes); else mbar_expect_tx_cluster(bar, stage_bytes);
                 for (int r0 = 0; r0 < row_n; r0 += box_rows) {
                     const int key = tile_start + r0, index = key >> page_shift;
@@ -508,7 +515,8 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     if (!mbar_wait(v_edge, edges & 1)) { ok = false; break; }
                     ++edges;
                     if (key0 + PR_BN > ctx) zero_value_rows<PR_BN>(dst, HD / 128, max(0, ctx - key0), PR_BN, 0, 1);
-                    if (key0 < key_lo) zero_value_rows<PR_BN>(dst, HD / 128, 0, min(PR_BN, key_lo - key0), 0, 1);
+                    // in front of the window's first key, but behind the kept keys
+                    if (key0 < key_lo) zero_value_rows<PR_BN>(dst, HD / 128, min(PR_BN, max(0, kept_cta - key0)), min(PR_BN, key_lo - key0), 0, 1);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     mbar_arrive_cluster_release(bar);
                 }
@@ -572,18 +580,26 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
         if (lane == 0) mbar_arrive_cluster(lead_q_full);
 
         const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
-        const int first_row = window > 0 ? max(0, pos_row - window + 1) : 0;
+        int first_row = window > 0 ? max(0, pos_row - window + 1) : 0, kept_row = 0;
+        if (keep > 0) { if (first_row <= keep) first_row = 0; else kept_row = keep; }
+        const float sc = capl > 0.f ? 1.0f : scale2;          // capped scores are in log2 units already
+        const float cap_in = capl > 0.f ? 2.0f * scale2 / capl : 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int n = 0; n < T; ++n) {
-            const int b = n & 1, ph = (n >> 1) & 1, key0 = (t0 + n) * PR_BN;
+            const int b = n & 1, ph = (n >> 1) & 1, key0 = tile_of(n) * PR_BN;
             if (!mbar_wait(s_full + 8 * b, ph)) { ok = false; break; }
             tc_fence_after();
             uint32_t sv[4][32];
 #pragma unroll
             for (int h = 0; h < 4; ++h) tc_ld32(t_lane + TC_S_COL + b * PR_BN + 32 * h, sv[h]);
             tc_wait_ld();
-            const bool inner = __all_sync(0xffffffffu, key0 + PR_BN - 1 <= pos_row && key0 >= first_row);
+            if (capl > 0.f) {      // tanh(x) = 1 - 2 / (1 + e^(2x)), x = score * scale / cap: two fast operations a score
+#pragma unroll
+                for (int c = 0; c < PR_BN; ++c)
+                    sv[c >> 5][c & 31] = __float_as_uint(capl * (1.0f - __fdividef(2.0f, 1.0f + __expf(__uint_as_float(sv[c >> 5][c & 31]) * cap_in))));
+            }
+            const bool inner = __all_sync(0xffffffffu, key0 + PR_BN - 1 <= pos_row && (key0 >= first_row || key0 + PR_BN <= kept_row));
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (inner) {
 #pragma unroll
@@ -592,13 +608,13 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
 #pragma unroll
                 for (int c = 0; c < PR_BN; ++c) {
                     const int key = key0 + c;
-                    const float v = (key <= pos_row && key >= first_row) ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
+                    const float v = (key <= pos_row && (key >= first_row || key < kept_row)) ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
                     sv[c >> 5][c & 31] = __float_as_uint(v);
                     mx4[c & 3] = fmaxf(mx4[c & 3], v);
                 }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            const float m_tile = fmaxf(m_run, mx * scale2);
+            const float m_tile = fmaxf(m_run, mx * sc);
             const float m_new = m_tile > m_run + TC_MAX_SLACK ? m_tile : m_run;      // lazily, as in the kernel above
             const float mbase = m_new == -INFINITY ? 0.f : m_new;
             const float corr = fast_exp2(m_run - mbase);
@@ -606,8 +622,8 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
             uint32_t packed[2][32];
 #pragma unroll
             for (int c = 0; c < PR_BN; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, -mbase));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), scale2, -mbase));
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sc, -mbase));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sc, -mbase));
                 sum4[(c >> 1) & 3] += p0 + p1;
                 packed[c >> 6][(c >> 1) & 31] = pack_bf16(p0, p1);
             }
