@@ -8,6 +8,7 @@
          window and beyond it, one key/value head, heads of 28 elements (held as 32 with zeros behind them)
 'odd'    sizes in no step of 4 or 8 (width 50, heads of 10 and 6, feed-forwards of 30, 14 and 10, nine experts), five streams,
          a layer with fewer query heads than the layer whose keys and values it reads
+'heads128'  heads of 128 elements, whose prompts of more than 64 tokens run on the tensor-memory attention of pairs of CTAs
 'plain'  no streams at all (a plain residual), no logit cap, one expert group kept of one, heads of 12 and 20 elements
 """
 from __future__ import annotations
@@ -88,8 +89,17 @@ ODD = {
     ],
 }
 
-CONFIGS = {"wide": WIDE, "one": ONE, "plain": PLAIN, "odd": ODD}
-SEEDS = {"wide": 21, "one": 22, "plain": 23, "odd": 24}
+HEADS128 = {
+    "architecture": "Taritar", "vocab": 120, "width": 64, "max_positions": 300, "streams": 2, "logit_softcap": 12.0,
+    "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "attention", "mixer": _att(4, 2, 128, None, (64, 10000.0), 0.08, 6.0, (40, 5)), "mlp": {"kind": "dense", "ff": 40, "limit": 1.0}},
+        {"type": "attention", "mixer": _att(4, 2, 128, None, (64, 10000.0), 0.08, 6.0, (23, 18), kv_from=0), "mlp": None},
+    ],
+}
+
+CONFIGS = {"wide": WIDE, "one": ONE, "plain": PLAIN, "odd": ODD, "heads128": HEADS128}
+SEEDS = {"wide": 21, "one": 22, "plain": 23, "odd": 24, "heads128": 25}
 
 
 def write_folder(folder: str, name: str, dtype=torch.bfloat16) -> str:

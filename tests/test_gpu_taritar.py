@@ -117,6 +117,28 @@ def test_long_decoding_passes_every_window_and_gives_pages_back(setups, name, dt
     runner.cache.close(rc)
 
 
+def test_long_portions_behind_released_pages_on_the_tensor_memory_attention(setups):
+    """Heads of 128 elements: a portion of more than 64 tokens runs on pairs of CTAs (tcgen05).  The second portion comes when
+    the window has passed pages that were given back (and hold NaN): it walks the kept keys' tile, then the window's."""
+    from wllm_b200.engine import StepEntry
+    folder = setups["heads128"][0]
+    reqs = requests_of("heads128", (260,), seed=12)
+    ref = plain_rows(folder, "heads128", reqs)
+    runner = runner_for(folder, torch.bfloat16, 16, 17)
+    rc = runner.cache.open("r0")
+    rows, pos = {}, 0
+    for n in (100, 130, 1, 29):
+        toks = reqs["r0"][pos:pos + n]
+        logits = runner.step([StepEntry(rc, toks, list(range(n)))]).float().cpu()
+        rows.update({("r0", pos + i): row for i, row in enumerate(logits)})
+        pos += n
+        if pos == 100:
+            assert rc.tables[0][0] >= 0 and rc.tables[0][1] >= 0 and rc.tables[0][2] == -1     # kept keys stay, the window passed a page
+    close_enough(rows, ref, torch.bfloat16)
+    from wllm_b200.kernels import ops
+    assert ops.tc_gemm_status(DEV) == 0
+
+
 def test_decoding_from_captured_graphs_gives_the_eager_rows(setups):
     folder, reqs, ref = setups["wide"]
     some = {k: reqs[k] for k in ("r1", "r2", "r5")}
