@@ -731,7 +731,8 @@ def taritar_bench(args) -> int:
             ms, launches, _, clocks, _ = decode_run(model, engine_cfg, args.batch, context, min(args.steps, 32), args.warmup, ps, 3)
             res[label] = {"weights_gb": round(model.weight_bytes() / 1e9, 3), "prefill_tok_s": round(T / (pre_ms / 1e3), 1),
                           "prefill_ms": round(pre_ms, 3), "decode_tok_s": round(args.batch / (ms / 1e3), 1),
-                          "decode_ms_per_step": round(ms, 4), "decode_launches": launches, "clocks": clocks}
+                          "decode_ms_per_step": round(ms, 4), "decode_launches": launches,
+                          "decode_weights_hbm_frac": round(model.weight_bytes() / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3), "clocks": clocks}
             del model
             torch.cuda.empty_cache()
         sizes[name] = {"shape": size, "models": res}
