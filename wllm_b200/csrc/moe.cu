@@ -13,6 +13,8 @@
 //            from the tokens' rows), then y = down_e act, 32-bit accumulation, each output one ascending chain over k.
 //            A CTA takes a tile of rows of ONE expert and a tile of columns; the grid is sized from the pair count
 //            and E alone (tiles that find no rows leave at once), so a captured step can replay it.
+//            Steps of many rows run these products on the tensor-memory kernel instead (gemm_bf16_tc.cu, grouped), over the
+//            tokens' rows copied into sorted order (moe_gather) and the table of row tiles that the plan writes.
 //   combine  out[token] = sum over the token's ranks, in rank order, of weight * y[place] (+ gate * shared unit).
 //
 // The gated unit is the clamped one: g = min(gate, limit), u = clamp(up, -limit, limit), g sigmoid(slope g) (u + 1).

@@ -9,8 +9,9 @@ unit's output is multiplied by sigmoid(row . x)).
 
 Router logits, the softmax over all experts, the choice and the weights (the chosen experts' scores as they are) are
 32-bit, against a 32-bit copy of the router matrix.  The tokens' (token, rank) pairs are sorted by expert on the device
-and the experts run as two grouped products over the sorted rows (csrc/moe.cu); a token's output is the sum over its
-ranks in rank order, so it does not depend on the batch.  Nothing comes back to the host, and every launch is sized
+and the experts run as two grouped products over the sorted rows (csrc/moe.cu; from `TC_FROM_PAIRS` pairs on, under
+bfloat16, on the grouped form of the tensor-memory product, csrc/gemm_bf16_tc.cu); a token's output is the sum over its
+ranks in rank order, so it does not depend on the batch beyond the rounding of the products.  Nothing comes back to the host, and every launch is sized
 from the number of tokens and experts alone.
 """
 from __future__ import annotations
