@@ -402,11 +402,11 @@ def test_experts_as_grouped_products(n, E, top, H, I, dtype):
     assert torch.equal(few.cpu(), out.cpu()[:m])
 
 
-@pytest.mark.parametrize("hd", [32, 48, 64, 128])
+@pytest.mark.parametrize("hd,n0", [(32, 236), (48, 236), (64, 236), (64, 150), (128, 236), (128, 90)])
 @pytest.mark.parametrize("size,keep,cap", [(40, 5, 6.0), (90, 33, 0.0), (16, 16, 18.0), (8, 70, 4.0), (64, 0, 2.5), (130, 1, 0.0), (100, 64, 3.0)])
-def test_tensor_core_attention_with_a_cap_and_kept_first_keys(size, keep, cap, hd):
-    """The bfloat16 kernels on mma.sync that walk a list of key tiles (the kept keys' tiles, then the window's): a prompt's
-    portion and decoded rows, with one key standing out at every edge, pages in scrambled order, page sizes 16 and 64, keys
+def test_tensor_core_attention_with_a_cap_and_kept_first_keys(size, keep, cap, hd, n0):
+    """The bfloat16 kernels (mma.sync and tcgen05) that walk a list of key tiles (the kept keys' tiles, then the window's): a
+    prompt's portion and decoded rows, with one key standing out at every edge, pages in scrambled order, page sizes 16 and 64, keys
     cut into several splits."""
     from wllm_b200.kernels import ops
     g = torch.Generator().manual_seed(size * 7 + keep + hd)
@@ -414,7 +414,8 @@ def test_tensor_core_attention_with_a_cap_and_kept_first_keys(size, keep, cap, h
     scale = 0.4 * (16 / hd) ** 0.5
     k = torch.randn(L, G, hd, generator=g).to(dtype)
     v = torch.randn(L, G, hd, generator=g).to(dtype)
-    n0 = 236 if hd != 128 else 90          # head size 128 and more than 128 rows: the prompt's rows run on pairs of CTAs (tcgen05)
+    # head sizes 32 and 48: mma.sync; 64 and 128: the tensor-memory kernel of one CTA a tile of 128 rows (n0 = 236: one tile, 150:
+    # three); 128 with more than 128 rows (n0 = 90): pairs of CTAs
     positions = list(range(n0, L))
     q = torch.randn(len(positions), H, hd, generator=g).to(dtype)
     one = lambda x: torch.tensor([x], dtype=torch.int32, device=DEV)

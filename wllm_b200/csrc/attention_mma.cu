@@ -1081,7 +1081,7 @@ WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void
 #if (HEAD_DIM % 64 == 0)
 #if (HEAD_DIM % 128 == 0)
     // more than one tile of 128 rows in the longest request: pairs of CTAs on 256-row tiles
-    // (the pair kernel walks a list of key tiles too and takes the cap; the one-CTA tensor-memory kernel does not)
+    // (the tensor-memory kernels walk a list of key tiles too and take the cap; a launch with kept keys shares no tile)
     if (use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         const int pair_tiles = (max_q_len * (nq / nkv) + 2 * TC_BM - 1) / (2 * TC_BM);
         return wllm_launch(prefill_pair_kernel, dim3(2 * nkv, requests, pair_tiles), TC_THREADS, PR_SMEM, stream,
@@ -1090,8 +1090,9 @@ WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void
                            cap * LOG2E, keep);
     }
 #endif
-    if (!listed && use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+    if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         int* arrivals = nullptr;
+        if (listed) split_above = 0;
         if (split_above > 0) {
             if (halves == nullptr || ((uintptr_t)halves & 15) || (long long)tiles * nkv * requests > ARRIVAL_SLOTS) return WLLM_BAD_SIZE;
             arrivals = tile_arrivals_address();
@@ -1100,7 +1101,7 @@ WLLM_API int wllm_attention_mma_prefill_capped(const void* q, int q_stride, void
         return wllm_launch(prefill_tc_kernel, dim3(nkv, requests, split_above > 0 ? 2 * tiles : tiles), TC_THREADS, TC_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                            block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, split_above, halves,
-                           arrivals, status, sinks);
+                           arrivals, status, sinks, cap * LOG2E, keep);
     }
 #endif
     return wllm_launch(prefill_kernel, dim3(nkv, requests, tiles), PRE_THREADS, PRE_SMEM, stream,

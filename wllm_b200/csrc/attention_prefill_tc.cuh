@@ -50,7 +50,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                   const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                   const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
                   int skip_single, int split_above, float* __restrict__ halves, int* __restrict__ arrivals,
-                  int* __restrict__ status, const float* __restrict__ sinks) {
+                  int* __restrict__ status, const float* __restrict__ sinks, float capl, int keep) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ int s_second;
     pdl_begin();
@@ -78,15 +78,24 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
 
     const int last_row = min(rows, row0 + TC_BM) - 1;
     const int pos_hi = pos0 + last_row / rep, pos_lo = pos0 + row0 / rep;
-    const int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, key_hi = pos_hi + 1;
+    int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, kept_cta = 0;
+    const int key_hi = pos_hi + 1;
+    // `keep` > 0: a sequence's first keys stay visible behind the window.  Where they touch the window the keys are one run from
+    // 0; else the tiles of the kept keys that lie before the window's first tile are walked first: place n of the walk is
+    // tile n, or t0 + n - head_tiles (such launches share no tile between two CTAs).  `capl` > 0: scores (log2 units)
+    // become capl * tanh(score / capl).
+    if (keep > 0) { if (key_lo <= keep) key_lo = 0; else kept_cta = keep; }
     int t0 = key_lo / TC_BN, t1 = (key_hi + TC_BN - 1) / TC_BN, T = t1 - t0;
-    const bool shared_tile = split_above > 0 && T > split_above;
+    const bool shared_tile = split_above > 0 && T > split_above && kept_cta == 0;
     if (!shared_tile && part == 1) return;
     if (shared_tile) {          // both halves hold keys of every row: a tile spans at most two key tiles of positions
         const int mid = t0 + (T + 1) / 2;
         if (part == 0) t1 = mid; else t0 = mid;
         T = t1 - t0;
     }
+    const int head_tiles = kept_cta > 0 ? min((kept_cta + TC_BN - 1) / TC_BN, t0) : 0;
+    T += head_tiles;
+    auto tile_of = [&](int n) { return n < head_tiles ? n : t0 + n - head_tiles; };
     const int page_shift = 31 - __clz(page_size);
     const int* table = block_table + (size_t)r * max_pages;
 
@@ -120,7 +129,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             bool ok = true;
             int n = 0;
             for (; n < T && ok; ++n) {
-                const int s = n % TC_KV_STAGES, ph = (n / TC_KV_STAGES) & 1, tile_start = (t0 + n) * TC_BN;
+                const int s = n % TC_KV_STAGES, ph = (n / TC_KV_STAGES) & 1, tile_start = tile_of(n) * TC_BN;
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
                 const uint32_t bar = full0 + 8 * s, dst = ring + s * TC_KV_BYTES;
                 mbar_expect_tx(bar, TC_KV_BYTES);
@@ -203,11 +212,14 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         }
 
         const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
-        const int first_row = window > 0 ? max(0, pos_row - window + 1) : 0;
+        int first_row = window > 0 ? max(0, pos_row - window + 1) : 0, kept_row = 0;
+        if (keep > 0) { if (first_row <= keep) first_row = 0; else kept_row = keep; }
+        const float sc = capl > 0.f ? 1.0f : scale2;          // capped scores are in log2 units already
+        const float cap_in = capl > 0.f ? 2.0f * scale2 / capl : 0.f;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int n = 0; n < T; ++n) {
-            const int b = n & 1, ph = (n >> 1) & 1, key0 = (t0 + n) * TC_BN;
+            const int b = n & 1, ph = (n >> 1) & 1, key0 = tile_of(n) * TC_BN;
             if (!mbar_wait(s_full + 8 * b, ph)) { ok = false; break; }
             tc_fence_after();
             uint32_t sv[2][32];
@@ -217,7 +229,12 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             // Scores stay unscaled until the exponent: max(scale * s) = scale * max(s) for scale > 0, and
             // exp2(scale * s - scale * m) is one fused multiply-add and one ex2 per element.  Only tiles at the
             // causal edge or the window's start need the per-key mask; the warp decides together.
-            const bool inner = __all_sync(0xffffffffu, key0 + TC_BN - 1 <= pos_row && key0 >= first_row);
+            if (capl > 0.f) {      // tanh(x) = 1 - 2 / (1 + e^(2x)), x = score * scale / cap: two fast operations a score, before the mask
+#pragma unroll
+                for (int c = 0; c < 64; ++c)
+                    sv[c >> 5][c & 31] = __float_as_uint(capl * (1.0f - __fdividef(2.0f, 1.0f + __expf(__uint_as_float(sv[c >> 5][c & 31]) * cap_in))));
+            }
+            const bool inner = __all_sync(0xffffffffu, key0 + TC_BN - 1 <= pos_row && (key0 >= first_row || key0 + TC_BN <= kept_row));
             // One warp runs alone on its scheduler, so a chain of dependent maxima or additions would cost its
             // full latency per element: four independent chains each (the order is fixed all the same).
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -228,7 +245,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int key = key0 + c;
-                    const float v = (key <= pos_row && key >= first_row) ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
+                    const float v = (key <= pos_row && (key >= first_row || key < kept_row)) ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
                     sv[c >> 5][c & 31] = __float_as_uint(v);
                     mx4[c & 3] = fmaxf(mx4[c & 3], v);
                 }
@@ -238,7 +255,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             // maximum has grown by more than TC_MAX_SLACK (in units of log2), so the probabilities stay below
             // 2^slack and the row of O has to be rescaled in few tiles instead of in most.  The quotient O / l
             // does not depend on the reference point.
-            const float m_tile = fmaxf(m_run, mx * scale2);
+            const float m_tile = fmaxf(m_run, mx * sc);
             const float m_new = m_tile > m_run + TC_MAX_SLACK ? m_tile : m_run;      // m_run = -inf: takes m_tile
             const float mbase = m_new == -INFINITY ? 0.f : m_new;
             const float corr = fast_exp2(m_run - mbase);
@@ -246,8 +263,8 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             uint32_t packed[32];
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, -mbase));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), scale2, -mbase));
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), sc, -mbase));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), sc, -mbase));
                 sum4[(c >> 1) & 3] += p0 + p1;
                 packed[c >> 1] = pack_bf16(p0, p1);
             }
@@ -264,7 +281,8 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                 if (!mbar_wait(v_full + 8 * vs, (n / TC_KV_STAGES) & 1)) { ok = false; break; }
                 const uint32_t vt = v_s + vs * TC_KV_BYTES;
                 if (key0 + TC_BN > ctx) zero_value_rows<TC_BN>(vt, HD / 64, max(0, ctx - key0), TC_BN, threadIdx.x - 64, 128);
-                if (key0 < key_lo) zero_value_rows<TC_BN>(vt, HD / 64, 0, min(TC_BN, key_lo - key0), threadIdx.x - 64, 128);
+                // in front of the window's first key, but behind the kept keys
+                if (key0 < key_lo) zero_value_rows<TC_BN>(vt, HD / 64, min(TC_BN, max(0, kept_cta - key0)), min(TC_BN, key_lo - key0), threadIdx.x - 64, 128);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             if (n > 0) {
