@@ -98,7 +98,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ w_router, co
         __syncwarp();
         // the groups that stay: groups_kept times the best one left (ties: the lower index); the others' experts leave
         if (groups_kept < groups) {
-            for (int round = 0; round < groups_kept; ++round) {
+            for (int pick = 0; pick < groups_kept; ++pick) {
                 float best = -INFINITY; int at = 0x7fffffff;
                 for (int g = lane; g < groups; g += 32) { const float v = gs[g]; if (v > best) { best = v; at = g; } }
                 for (int o = 16; o > 0; o >>= 1) {
